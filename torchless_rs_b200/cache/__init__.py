@@ -1,6 +1,7 @@
 from .pages import CacheCapacityError, CacheRollbackError, CacheStateError, FreeList
-from .requests import PagedKVRequest, StateRequest
-from .cache import PAGE, Cache, PagedGroup, PagedView, StateGroup, pages_for
+from .requests import PagedKVRequest, PagedLatentRequest, StateRequest
+from .cache import PAGE, Cache, LatentView, PagedGroup, PagedView, StateGroup, pages_for
 
-__all__ = ["CacheCapacityError", "CacheRollbackError", "CacheStateError", "FreeList", "PagedKVRequest", "StateRequest",
-           "PAGE", "Cache", "PagedGroup", "PagedView", "StateGroup", "pages_for"]
+__all__ = ["CacheCapacityError", "CacheRollbackError", "CacheStateError", "FreeList", "PagedKVRequest",
+           "PagedLatentRequest", "StateRequest", "PAGE", "Cache", "LatentView", "PagedGroup", "PagedView",
+           "StateGroup", "pages_for"]

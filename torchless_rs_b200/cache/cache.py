@@ -27,7 +27,7 @@ import torch
 
 from ..csrc.build import PAGE_TOKENS
 from .pages import CacheCapacityError, CacheRollbackError, CacheStateError, FreeList
-from .requests import PagedKVRequest, StateRequest
+from .requests import PagedKVRequest, PagedLatentRequest, StateRequest
 
 PAGE = PAGE_TOKENS   # tokens per cache page: the number the kernels were compiled with
 
@@ -46,16 +46,32 @@ class PagedView:
     group: "PagedGroup"
 
 
+@dataclass
+class LatentView:
+    """What a latent-attention mixer gets for its layer."""
+    pages: torch.Tensor         # [pages, PAGE, width]
+    page_table: torch.Tensor    # [slots, pages per sequence] int32, on the device
+    window: Optional[int]
+    group: "PagedGroup"
+
+
 class PagedGroup:
-    def __init__(self, request: PagedKVRequest, layers: Sequence[int], n_pages: int,
-                 max_slots: int, table_width: int, dtype: torch.dtype, device: torch.device):
+    """Pages of one kind of content (keys and values per head, or one latent vector per
+    position) with their pool and page table; what a page holds does not matter to the
+    bookkeeping."""
+
+    def __init__(self, request: Union[PagedKVRequest, PagedLatentRequest], layers: Sequence[int],
+                 n_pages: int, max_slots: int, table_width: int, dtype: torch.dtype,
+                 device: torch.device):
         self.request = request
         self.layers = list(layers)
         self.n_pages = n_pages
         self.pool = FreeList(n_pages, "cache page")
-        self.storage = torch.zeros(
-            (len(self.layers), 2, n_pages, request.num_kv_heads, PAGE * request.head_dim),
-            dtype=dtype, device=device)
+        if isinstance(request, PagedLatentRequest):
+            shape = (len(self.layers), n_pages, PAGE * request.width)
+        else:
+            shape = (len(self.layers), 2, n_pages, request.num_kv_heads, PAGE * request.head_dim)
+        self.storage = torch.zeros(shape, dtype=dtype, device=device)
         self.table_host = np.full((max_slots, table_width), -1, dtype=np.int32)
         self.table_dev = torch.full((max_slots, table_width), -1, dtype=torch.int32, device=device)
         self.first_live = [0] * max_slots   # first table column that still holds a page
@@ -159,9 +175,12 @@ class PagedGroup:
             ev.record()
             self._staging_events[self._turn] = ev
 
-    def view(self, layer: int) -> PagedView:
+    def view(self, layer: int):
         i = self.layers.index(layer)
         r = self.request
+        if isinstance(r, PagedLatentRequest):
+            return LatentView(self.storage[i].view(self.n_pages, PAGE, r.width), self.table_dev,
+                              r.window, self)
         k = self.storage[i, 0].view(self.n_pages, r.num_kv_heads, PAGE, r.head_dim)
         v = self.storage[i, 1].view(self.n_pages, r.num_kv_heads, r.head_dim, PAGE)
         return PagedView(k, v, self.table_dev, r.window, self)
@@ -188,7 +207,7 @@ class Cache:
     (None: nothing, or it reads another entry's cache); "layer" below means such an entry.  `max_tokens` is the most tokens that live sequences hold
     at any time, each sequence's count rounded up to a multiple of PAGE."""
 
-    def __init__(self, requests: Sequence[Union[PagedKVRequest, StateRequest, None]],
+    def __init__(self, requests: Sequence[Union[PagedKVRequest, PagedLatentRequest, StateRequest, None]],
                  max_tokens: int, max_slots: Optional[int] = None,
                  max_seq_len: Optional[int] = None, dtype: torch.dtype = torch.bfloat16,
                  device: Union[str, torch.device] = "cuda"):
@@ -209,7 +228,7 @@ class Cache:
             if req is not None:
                 by_request.setdefault(req, []).append(layer)
         for req, layers in by_request.items():
-            if isinstance(req, PagedKVRequest):
+            if isinstance(req, (PagedKVRequest, PagedLatentRequest)):
                 g = PagedGroup(req, layers, n_pages, self.max_slots, table_width, dtype, self.device)
                 self.paged.append(g)
             elif isinstance(req, StateRequest):

@@ -18,6 +18,14 @@ class PagedKVRequest:
 
 
 @dataclass(frozen=True)
+class PagedLatentRequest:
+    """One vector of `width` numbers per position, shared by all heads (the compressed keys
+    and values of latent attention), of every position or of the last `window` only."""
+    width: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
 class StateRequest:
     """Per-sequence state of fixed size, zero when a sequence starts."""
     shape: Tuple[int, ...]

@@ -35,10 +35,12 @@ def _name_of(data: dict) -> str:
     archs = data.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
-    mt = data.get("model_type")
-    if isinstance(mt, str):
-        return mt
-    raise ConfigError("config.json: neither 'architectures' nor 'model_type' names the architecture")
+    for key in ("model_type", "architecture"):
+        name = data.get(key)
+        if isinstance(name, str):
+            return name
+    raise ConfigError("config.json: none of 'architectures', 'model_type' and 'architecture' names the "
+                      "architecture")
 
 
 def config_from_dict(data: dict, where: str = "config.json"):
@@ -57,6 +59,8 @@ def load_config(model_dir: str):
 def _register_builtin() -> None:
     from .mistral import MistralConfig
     register_architecture("MistralForCausalLM", "mistral", "mistralai")(MistralConfig)
+    from .kikopel import KikopelConfig
+    register_architecture("Kikopel")(KikopelConfig)
 
 
 _register_builtin()

@@ -70,6 +70,8 @@ class ModelSpec:
     position_table_name: Optional[str] = None    # a learned table [max_positions, hidden] whose row
     max_positions: int = 0                       #   at each token's position is added to the stream
     logit_softcap: Optional[float] = None        # logits <- cap * tanh(logits / cap)
+    embedding_addend: Optional[PartSpec] = None  # a registered part that adds to the embedded tokens
+                                                 #   (it may keep per-sequence state)
 
     def validate(self) -> None:
         from .errors import ConfigError

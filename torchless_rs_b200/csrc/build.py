@@ -31,10 +31,13 @@ PAGE_TOKENS = 64
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
               f"-DTL_PAGE={PAGE_TOKENS}"]
 
+_CORE_SOURCES = ("elementwise.cu", "gemm_generic.cu", "attention_generic.cu", "branch_elementwise.cu",
+                 "latent_attention.cu", "linear_recurrence.cu")
+
 # library name -> (sources, defines)
 LIBRARIES: Dict[str, Tuple[Sequence[str], Sequence[str]]] = {
-    "core_f32": (("elementwise.cu", "gemm_generic.cu", "attention_generic.cu"), ("-DTL_DTYPE=0",)),
-    "core_bf16": (("elementwise.cu", "gemm_generic.cu", "attention_generic.cu"), ("-DTL_DTYPE=1",)),
+    "core_f32": (_CORE_SOURCES, ("-DTL_DTYPE=0",)),
+    "core_bf16": (_CORE_SOURCES, ("-DTL_DTYPE=1",)),
     "sampling": (("sampling.cu",), ()),
     "random_init": (("random_init.cu",), ()),
 }

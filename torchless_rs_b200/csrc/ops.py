@@ -122,7 +122,8 @@ class CoreOps:
         self.suffix = _SUFFIX[act_dtype]
         self.lib = build.load_library(f"core_{self.suffix}")
         for base in ("tl_embed", "tl_softcap", "tl_advance_step", "tl_regroup_step", "tl_convert", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
-                     "tl_gemm_generic", "tl_attn_generic"):
+                     "tl_gemm_generic", "tl_attn_generic", "tl_pair_embed_add", "tl_branch_norm_add", "tl_poly_norm",
+                     "tl_latent_prep", "tl_headwise_gemm", "tl_latent_attn", "tl_gated_scan"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
             setattr(self, "_" + base, fn)
@@ -288,6 +289,150 @@ class CoreOps:
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(token_pos), _ptr(token_seq),
             _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)), c_int(T), c_int(nh),
             c_int(nkv), c_int(hd), c_int(window or 0), c_float(scale), _stream()), "attn_generic")
+
+    # ---- sublayers that read the stream itself, with the norm on their output -------------------
+    def pair_embed_add(self, batch_tokens: torch.Tensor, token_from: Optional[torch.Tensor],
+                       token_src: Optional[torch.Tensor], token_pos: torch.Tensor, token_seq: torch.Tensor,
+                       seq_slot: torch.Tensor, seq_start: torch.Tensor, last_token: torch.Tensor,
+                       table: torch.Tensor, x: torch.Tensor, vocab: int, buckets: int, mul_prev: int,
+                       mul_cur: int) -> None:
+        """x[t] += table[(prev * mul_prev + token * mul_cur) mod buckets], the table's last row for a
+        sequence's first token; `last_token` ([slots] int32) holds every sequence's latest token and is
+        brought up to date (a second kernel)."""
+        from ctypes import c_longlong
+        _need(table, self.act_dtype, "pair table")
+        _need(x, torch.float32, "pair embed stream")
+        _need(last_token, torch.int32, "last tokens")
+        T, H = x.shape
+        if table.shape != (buckets + 1, H):
+            raise KernelError("pair_embed_add: the table must have buckets + 1 rows of the stream's width")
+        _check(self._tl_pair_embed_add(
+            _ptr(batch_tokens), _ptr(token_from if token_src is not None else None), _ptr(token_src),
+            _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(seq_start), _ptr(last_token), _ptr(table),
+            _ptr(x), c_int(T), c_int(seq_slot.numel()), c_int(H), c_int(vocab), c_int(buckets),
+            c_longlong(mul_prev), c_longlong(mul_cur), _stream()), "pair_embed_add")
+        _check(0, "remember_last_token")
+
+    def branch_norm_add(self, y: torch.Tensor, gain: torch.Tensor, mult: float, eps: float, x: torch.Tensor,
+                        xb: Optional[torch.Tensor] = None) -> None:
+        """x += mult * gain * y / rms(y), row by row, `gain` one 32-bit number on the device; `xb`
+        (activation type) also receives the new x."""
+        _need(y, torch.float32, "branch output", contiguous=False)
+        _need(x, torch.float32, "stream")
+        _need(gain, torch.float32, "branch gain")
+        rows, H = x.shape
+        if y.shape != x.shape or y.stride(1) != 1 or gain.numel() != 1:
+            raise KernelError("branch_norm_add: sizes do not match")
+        if xb is not None:
+            _need(xb, self.act_dtype, "stream copy")
+        _check(self._tl_branch_norm_add(_ptr(y), c_int(y.stride(0)), _ptr(gain), c_float(mult), c_float(eps),
+                                        _ptr(x), _ptr(xb), c_int(rows), c_int(H), _stream()), "branch_norm_add")
+
+    def poly_norm(self, z: torch.Tensor, coeff: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+        """out = a N(z) + b N(z^2) + c N(z^3) + e per row, coeff = (a, b, c, e) 32-bit on the device."""
+        _need(z, torch.float32, "poly_norm in", contiguous=False)
+        _need(out, self.act_dtype, "poly_norm out")
+        _need(coeff, torch.float32, "poly_norm coefficients")
+        rows, F = out.shape
+        if z.shape != out.shape or z.stride(1) != 1 or coeff.numel() != 4:
+            raise KernelError("poly_norm: sizes do not match")
+        _check(self._tl_poly_norm(_ptr(z), c_int(z.stride(0)), _ptr(coeff), c_float(eps), _ptr(out), c_int(rows),
+                                  c_int(F), _stream()), "poly_norm")
+
+    # ---- attention through latents ----------------------------------------------------------------
+    def latent_prep(self, dq: torch.Tensor, dkv: torch.Tensor, wq: torch.Tensor, wc: torch.Tensor, eps: float,
+                    cq: torch.Tensor, pages: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+                    seq_slot: torch.Tensor, page_table: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                    rank: int, rot: int, dims: int) -> None:
+        """cq = norm(dq) * wq; the token's page row = [norm(dkv[:, :rank]) * wc | rotate(dkv[:, rank:])]."""
+        for t, n in ((dq, "query down-projection"), (dkv, "key/value down-projection")):
+            _need(t, torch.float32, n, contiguous=False)
+            if t.stride(1) != 1:
+                raise KernelError(f"latent_prep: {n} must have contiguous rows")
+        _need(wq, torch.float32, "query latent norm weight")
+        _need(wc, torch.float32, "latent norm weight")
+        _need(cq, self.act_dtype, "query latent")
+        _need(pages, self.act_dtype, "latent pages")
+        _need(page_table, torch.int32, "page table")
+        T, q_rank = cq.shape
+        if dq.shape != (T, q_rank) or dkv.shape != (T, rank + rot) or wq.numel() != q_rank or \
+                wc.numel() != rank or pages.shape[1:] != (PAGE, rank + rot):
+            raise KernelError("latent_prep: sizes do not match")
+        if dims:
+            _need(inv_freq, torch.float32, "inv_freq")
+            if inv_freq.numel() != dims // 2:
+                raise KernelError("latent_prep: inv_freq must have dims/2 entries")
+        _check(self._tl_latent_prep(
+            _ptr(dq), c_int(dq.stride(0)), _ptr(dkv), c_int(dkv.stride(0)), _ptr(wq), _ptr(wc), c_float(eps),
+            _ptr(cq), _ptr(pages), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table),
+            c_int(page_table.stride(0)), _ptr(inv_freq if dims else None), c_int(T), c_int(q_rank), c_int(rank),
+            c_int(rot), c_int(dims), _stream()), "latent_prep")
+
+    def headwise_gemm(self, a: torch.Tensor, a_head: int, w: torch.Tensor, c: torch.Tensor, c_head: int,
+                      gate: Optional[torch.Tensor] = None) -> None:
+        """c[t, h * c_head + n] = sum_k a[t, h * a_head + k] * w[h, n, k] for every head h; with `gate`
+        ([T, heads * N] 32-bit) the result is multiplied by sigmoid(gate) and `c` is of the activation
+        type, else `c` is 32-bit."""
+        _need(a, torch.float32, "headwise a", contiguous=False)
+        _need(w, self.act_dtype, "headwise w")
+        _need(c, torch.float32 if gate is None else self.act_dtype, "headwise c", contiguous=False)
+        heads, N, K = w.shape
+        M = a.shape[0]
+        if a.stride(1) != 1 or c.stride(1) != 1 or c.shape[0] != M or \
+                a.shape[1] < (heads - 1) * a_head + K or c.shape[1] < (heads - 1) * c_head + N:
+            raise KernelError("headwise_gemm: sizes do not match")
+        ldg = 0
+        if gate is not None:
+            _need(gate, torch.float32, "headwise gate", contiguous=False)
+            if gate.shape != (M, heads * N) or gate.stride(1) != 1:
+                raise KernelError("headwise_gemm: the gate must be [rows, heads * outputs]")
+            ldg = gate.stride(0)
+        _check(self._tl_headwise_gemm(_ptr(a), c_int(a.stride(0)), c_int(a_head), _ptr(w), _ptr(c),
+                                      c_int(c.stride(0)), c_int(c_head), _ptr(gate), c_int(ldg), c_int(M), c_int(N),
+                                      c_int(K), c_int(heads), c_int(0 if gate is None else 1), _stream()),
+               "headwise_gemm")
+
+    def latent_attn(self, qa: torch.Tensor, q: torch.Tensor, q_head: int, q_off: int, pages: torch.Tensor,
+                    out: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
+                    page_table: torch.Tensor, inv_freq: Optional[torch.Tensor], heads: int, rank: int, rot: int,
+                    dims: int, window: Optional[int], scale: float) -> None:
+        """out[t, h, :] = softmax over the visible positions of ((qa[t, h] . c + rotate(q_rot[t, h]) . r) *
+        scale) times the positions' c; page rows are [c | r]."""
+        _need(qa, torch.float32, "latent queries")
+        _need(q, torch.float32, "queries", contiguous=False)
+        _need(pages, self.act_dtype, "latent pages")
+        _need(out, torch.float32, "latent attention out")
+        _need(page_table, torch.int32, "page table")
+        T = qa.shape[0]
+        if qa.shape != (T, heads, rank) or out.shape != (T, heads, rank) or q.stride(1) != 1 or \
+                pages.shape[1:] != (PAGE, rank + rot) or q.shape[1] < (heads - 1) * q_head + q_off + rot:
+            raise KernelError("latent_attn: sizes do not match")
+        _check(self._tl_latent_attn(
+            _ptr(qa), _ptr(q), c_int(q.stride(0)), c_int(q_head), c_int(q_off), _ptr(pages), _ptr(out),
+            _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)),
+            _ptr(inv_freq if dims else None), c_int(T), c_int(heads), c_int(rank), c_int(rot), c_int(dims),
+            c_int(window or 0), c_float(scale), _stream()), "latent_attn")
+
+    # ---- gated linear recurrence ------------------------------------------------------------------
+    def gated_scan(self, z: torch.Tensor, bias: torch.Tensor, low: torch.Tensor, state: torch.Tensor,
+                   out: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor, heads: int, dim: int,
+                   vdim: int) -> None:
+        """The recurrence S <- diag(f) S + (1 - f) v^T, o = S^T q over each sequence's tokens of the step,
+        from and into `state` [slots, heads, dim, vdim]; `z` [T, 2 heads dim + heads vdim] 32-bit holds the
+        projections for q, f and v side by side."""
+        _need(z, torch.float32, "recurrence projections", contiguous=False)
+        for t, n in ((bias, "forget bias"), (low, "forget lower bound"), (state, "recurrent state"),
+                     (out, "recurrence out")):
+            _need(t, torch.float32, n)
+        T = z.shape[0]
+        hd = heads * dim
+        if z.shape[1] != 2 * hd + heads * vdim or z.stride(1) != 1 or out.shape != (T, heads * vdim) or \
+                bias.numel() != hd or low.numel() != hd or state.shape[1:] != (heads, dim, vdim):
+            raise KernelError("gated_scan: sizes do not match")
+        _check(self._tl_gated_scan(_ptr(z), _ptr(z[:, hd:]), _ptr(z[:, 2 * hd:]), c_int(z.stride(0)), _ptr(bias),
+                                   _ptr(low), _ptr(state), _ptr(out), c_int(out.stride(0)), _ptr(seq_start),
+                                   _ptr(seq_slot), c_int(seq_slot.numel()), c_int(heads), c_int(dim), c_int(vdim),
+                                   _stream()), "gated_scan")
 
 
 class SamplingOps:

@@ -36,6 +36,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
         spec.embedding_name: TensorSpec((spec.vocab_size, spec.hidden_size))}
     if spec.position_table_name is not None:
         out[spec.position_table_name] = TensorSpec((spec.max_positions, spec.hidden_size))
+    if spec.embedding_addend is not None:
+        out.update(lookup("embedding_addend", spec.embedding_addend.kind).expected_tensors(spec.embedding_addend))
     for layer in spec.layers:
         _block_class(layer)
         for table, ps, role in (
@@ -78,13 +80,16 @@ class DecoderModel:
             self.mixers.append(mixer)
         self.final_norm = lookup("norm", spec.final_norm.kind)(
             spec.final_norm, spec.final_norm_prefix, rt)
+        self.embedding_addend = (lookup("embedding_addend", spec.embedding_addend.kind)(spec.embedding_addend, rt)
+                                 if spec.embedding_addend is not None else None)
         self.embedding: Optional[torch.Tensor] = None
         self.position_table: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         # a part whose forward reads host-side values of the batch cannot be replayed from a
         # recorded graph; it says so by not setting `graph_safe`
         self.graph_safe = all(getattr(p, "graph_safe", False)
-                              for b in self.blocks for p in (b.mixer, b.feed_forward))
+                              for b in self.blocks for p in (b.mixer, b.feed_forward)) and \
+            (self.embedding_addend is None or getattr(self.embedding_addend, "graph_safe", False))
 
     @staticmethod
     def _parts_of(block) -> list:
@@ -98,6 +103,8 @@ class DecoderModel:
         self.embedding = self.rt.matrix(weights[self.spec.embedding_name])
         if self.spec.position_table_name is not None:
             self.position_table = self.rt.matrix(weights[self.spec.position_table_name])
+        if self.embedding_addend is not None:
+            self.embedding_addend.load(weights)
         for b in self.blocks:
             for part in self._parts_of(b):
                 part.load(weights)
@@ -113,19 +120,26 @@ class DecoderModel:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
         add(self.embedding); add(self.head); add(self.position_table)
-        for b in self.blocks:
-            for part in self._parts_of(b):
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor):
-                        add(v)
+        parts = [part for b in self.blocks for part in self._parts_of(b)]
+        if self.embedding_addend is not None:
+            parts.append(self.embedding_addend)
+        for part in parts:
+            for k, v in vars(part).items():
+                # a part names the attributes that view the cache's state, which are no weights
+                if isinstance(v, torch.Tensor) and k not in getattr(part, "state_attributes", ()):
+                    add(v)
         return total
 
     # ---- cache ------------------------------------------------------------------------
     # A cache belongs to a place in the order, not to a layer: a layer that is named twice
     # runs twice per token and keeps keys and values of both passes apart.
     def cache_requests(self) -> List[object]:
-        """One request per entry of the order (None where the entry keeps no cache)."""
-        return [self.mixers[i].cache_request() for i in self.spec.order]
+        """One request per entry of the order (None where the entry keeps no cache), then one for
+        what the embedding keeps per sequence, if it keeps anything."""
+        reqs = [self.mixers[i].cache_request() for i in self.spec.order]
+        if self.embedding_addend is not None:
+            reqs.append(self.embedding_addend.cache_request())
+        return reqs
 
     def bind_cache(self, cache) -> None:
         self.views = []
@@ -134,6 +148,8 @@ class DecoderModel:
             src = self.spec.layers[i].cache_from
             self.views.append(cache.view(k) if src is None else cache.view(last_run[src]))
             last_run[i] = k
+        if self.embedding_addend is not None:
+            self.embedding_addend.bind_cache(cache.view(len(self.spec.order)))
 
     # ---- one step -----------------------------------------------------------------------
     def forward(self, batch) -> Optional[torch.Tensor]:
@@ -145,6 +161,8 @@ class DecoderModel:
         rt.ops.embed(batch.tokens, self.embedding, x, batch.token_from, batch.token_src,
                      scale=self.spec.embedding_scale, position_table=self.position_table,
                      token_pos=batch.token_pos)
+        if self.embedding_addend is not None:
+            self.embedding_addend.forward(batch, x)
         order = self.spec.order
         carry = None
         for k, i in enumerate(order):

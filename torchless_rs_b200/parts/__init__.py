@@ -1,8 +1,9 @@
-from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, lookup, register_block,
-                       register_feed_forward, register_mixer, register_norm, register_position)
+from .registry import (BLOCKS, EMBEDDING_ADDENDS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, lookup, register_block,
+                       register_embedding_addend, register_feed_forward, register_mixer, register_norm, register_position)
 from .runtime import Runtime, Workspace
-from . import attention, block, feed_forward, norm, position  # registers the built-in parts
+from . import (attention, block, embedding, feed_forward, latent_attention, norm, position,  # registers
+               recurrence)                                                                   # the built-in parts
 
-__all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "lookup", "register_block",
-           "register_feed_forward", "register_mixer", "register_norm", "register_position",
+__all__ = ["BLOCKS", "EMBEDDING_ADDENDS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "lookup", "register_block",
+           "register_embedding_addend", "register_feed_forward", "register_mixer", "register_norm", "register_position",
            "Runtime", "Workspace"]

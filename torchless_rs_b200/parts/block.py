@@ -70,3 +70,85 @@ class PreNormBlock:
         else:
             self.feed_forward.forward(inp2, x, batch)
         return c3 if (c3 is not None and c3.valid) else None
+
+
+class StreamCopy:
+    """What a branch-norm block hands to the next one: the stream in the activation type, as the
+    kernel that last changed the stream wrote it.  (`valid` is False so that a block that expects the
+    prepared input of a norm ignores it.)"""
+    valid = False
+
+    def __init__(self, xb: torch.Tensor):
+        self.xb = xb
+
+
+@register_block("branchnorm")
+class BranchNormBlock:
+    """x <- x + m * norm_1(mixer(x)); x <- x + m * norm_2(feed_forward(x)): the sublayers read the
+    stream itself and the norm sits on each branch's output.  Parameter: `residual_mult` (m).
+
+    The branch writes its output to a 32-bit buffer; one kernel takes its root mean square, adds
+    m * gain * y / rms to the stream and writes the stream's copy in the activation type, which the next
+    sublayer's products read (in 32-bit the stream is that copy).  A sublayer that says
+    `can_overwrite` stores its output (`forward(..., overwrite=True)`); any other adds into the zeroed
+    buffer, so every registered mixer and feed-forward fits.  Norms: any with a single `gain`, or
+    with a `weight` per coordinate."""
+    norm_roles = ("mixer_out_norm", "feed_forward_out_norm")
+    takes_carry = True
+    first_norm = None   # no norm stands before this block's first product
+
+    def __init__(self, spec, rt: Runtime, mixer, feed_forward, norms):
+        self.rt = rt
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norms = dict(norms)
+        self.mult = float(spec.get("residual_mult", 1.0))
+        self._gains = {}
+
+    def _gain(self, norm):
+        g = getattr(norm, "gain", None)
+        if g is not None:
+            return g
+        key = id(norm)
+        if key not in self._gains:
+            self._gains[key] = norm.weight.to(torch.float32).contiguous()
+        return self._gains[key]
+
+    def _branch(self, part, norm, x, xb, batch):
+        rt = self.rt
+        y = rt.workspace.get("branch_out", x.shape, torch.float32)
+        if getattr(part, "can_overwrite", False):
+            part.forward(xb, y, batch, overwrite=True)
+        else:
+            y.zero_()
+            part.forward(xb, y, batch)
+        gain = self._gain(norm)
+        if gain.numel() != 1:
+            # a weight per coordinate: the norm's own kernel, then the scaled sum
+            yn = rt.workspace.get("branch_normed", x.shape, rt.act_dtype)
+            norm(y, yn)
+            x.add_(yn.to(torch.float32), alpha=self.mult)
+            if xb is not x:
+                xb.copy_(x)
+            return
+        rt.ops.branch_norm_add(y, gain, self.mult, norm.eps, x, None if xb is x else xb)
+
+    def forward(self, x: torch.Tensor, batch, carry=None, next_norm=None):
+        rt = self.rt
+        if rt.is_f32:
+            xb = x
+        elif isinstance(carry, StreamCopy) and carry.xb.shape == x.shape:
+            xb = carry.xb
+        else:
+            xb = rt.workspace.get("branch_in", x.shape, rt.act_dtype)
+            rt.ops.convert_into(x, xb)
+        self._branch(self.mixer, self.norms["mixer_out_norm"], x, xb, batch)
+        if "feed_forward_out_norm" in self.norms:
+            self._branch(self.feed_forward, self.norms["feed_forward_out_norm"], x, xb, batch)
+        return None if xb is x else StreamCopy(xb)
+
+
+@register_block("branchnorm_mixer_only")
+class BranchNormMixerBlock(BranchNormBlock):
+    """The same block for a layer without a feed-forward: x <- x + m * norm_1(mixer(x))."""
+    norm_roles = ("mixer_out_norm",)

@@ -54,3 +54,60 @@ class SwiGLU:
         act = self.rt.workspace.get("ffn_act", (T, self.inter), self.rt.act_dtype)
         self.matmul(xn, self.w_gate_up, act, ops.MODE_SWIGLU)
         self.matmul(act, self.w_down, residual, ops.MODE_ACCUM_F32, emit=emit)
+
+
+@register_feed_forward("polynorm")
+class PolyNormFeedForward:
+    """down( act(up x) ) with act(z) = a N(z) + b N(z^2) + c N(z^3) + e: powers element by element,
+    N the division of a token's vector by its root mean square (32-bit), and four learned numbers.
+    Parameters: `hidden_size`, `intermediate_size`, `eps`.  Tensors under the prefix: up, down, act."""
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, spec: PartSpec, prefix: str, rt: Runtime):
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.eps = float(spec.params["eps"])
+        self.prefix = prefix
+        self.rt = rt
+        self.matmul = Matmul(rt)
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorSpec]:
+        h, i = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        return {f"{prefix}.up": TensorSpec((i, h)), f"{prefix}.down": TensorSpec((h, i)),
+                f"{prefix}.act": TensorSpec((4,), init=(0.5, 0.3))}
+
+    def load(self, weights: Dict[str, torch.Tensor]) -> None:
+        p = self.prefix
+        self.w_up = self.rt.matrix(weights[f"{p}.up"])
+        self.w_down = self.rt.matrix(weights[f"{p}.down"])
+        self.coeff = weights[f"{p}.act"].to(device=self.rt.device, dtype=torch.float32).contiguous()
+
+    def forward(self, xn, residual: torch.Tensor, batch, emit=None, overwrite: bool = False) -> None:
+        rt, ws = self.rt, self.rt.workspace
+        T = residual.shape[0]
+        z = ws.get("ffn_pre", (T, self.inter), torch.float32)
+        self.matmul(xn, self.w_up, z, ops.MODE_STORE_F32)
+        act = ws.get("ffn_act", (T, self.inter), rt.act_dtype)
+        rt.ops.poly_norm(z, self.coeff, self.eps, act)
+        self.matmul(act, self.w_down, residual, ops.MODE_STORE_F32 if overwrite else ops.MODE_ACCUM_F32)
+
+
+@register_feed_forward("none")
+class NoFeedForward:
+    """A layer without a feed-forward: no tensors, and nothing is added."""
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, prefix: str, rt: Runtime):
+        pass
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorSpec]:
+        return {}
+
+    def load(self, weights) -> None:
+        pass
+
+    def forward(self, xn, residual, batch, emit=None) -> None:
+        pass

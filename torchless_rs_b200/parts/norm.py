@@ -37,3 +37,34 @@ class RMSNorm:
     def __call__(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         self.rt.ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
+
+
+@register_norm("rmsnorm_scalar")
+class ScalarRMSNorm:
+    """y = x / sqrt(mean(x^2) + eps) * g with one number g for all coordinates.  Parameters: `size`,
+    `eps`.  Its tensor is a single number stored under the norm's own name (no `.weight`).
+
+    Besides the interface of every norm it offers `gain` (g as a 32-bit tensor of one element on
+    the device), which a block that normalises a branch's output reads."""
+
+    foldable = False
+
+    def __init__(self, spec: PartSpec, prefix: str, rt: Runtime):
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.name = prefix
+        self.rt = rt
+        self.gain: Optional[torch.Tensor] = None
+        self.weight: Optional[torch.Tensor] = None
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorSpec]:
+        return {prefix: TensorSpec((), init=(0.1, 1.0))}
+
+    def load(self, weights: Dict[str, torch.Tensor]) -> None:
+        self.gain = weights[self.name].reshape(1).to(device=self.rt.device, dtype=torch.float32)
+        self.weight = self.gain.expand(self.size).contiguous()   # what the row kernel reads
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        self.rt.ops.rmsnorm(x, self.weight, self.eps, out, rows)
+        return out

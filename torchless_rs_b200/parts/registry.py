@@ -9,9 +9,10 @@ FEED_FORWARDS: Dict[str, type] = {}
 NORMS: Dict[str, type] = {}
 POSITIONS: Dict[str, type] = {}
 BLOCKS: Dict[str, type] = {}
+EMBEDDING_ADDENDS: Dict[str, type] = {}
 
 _TABLES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS,
-           "position": POSITIONS, "block": BLOCKS}
+           "position": POSITIONS, "block": BLOCKS, "embedding_addend": EMBEDDING_ADDENDS}
 
 
 def register(table: str, kind: str) -> Callable[[type], type]:
@@ -26,6 +27,7 @@ def register_feed_forward(kind: str): return register("feed_forward", kind)
 def register_norm(kind: str): return register("norm", kind)
 def register_position(kind: str): return register("position", kind)
 def register_block(kind: str): return register("block", kind)
+def register_embedding_addend(kind: str): return register("embedding_addend", kind)
 
 
 def lookup(table: str, kind: str) -> type:

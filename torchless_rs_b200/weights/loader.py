@@ -21,7 +21,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass
-from typing import Dict, Mapping, Tuple
+from typing import Dict, Mapping, Optional, Tuple
 
 import torch
 
@@ -35,9 +35,14 @@ _INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8, torch.b
 @dataclass(frozen=True)
 class TensorSpec:
     """What a part expects of one tensor: its exact shape, and whether it is a
-    table of integers."""
+    table of integers.  `init` = (standard deviation, mean) says how random weights draw it
+    where the shape alone does not (matrices N(0, 0.02), vectors 1 + N(0, 0.1)).  An
+    `optional` tensor may be absent from a folder; if present it is checked like the others
+    (random weights leave it out)."""
     shape: Tuple[int, ...]
     integer: bool = False
+    init: Optional[Tuple[float, float]] = None
+    optional: bool = False
 
 
 def storage_dtype(stored: torch.dtype, run_dtype: torch.dtype = torch.bfloat16) -> torch.dtype:
@@ -114,7 +119,7 @@ class WeightSource:
 def check_against(source_name: str, have: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]],
                   expected: Mapping[str, TensorSpec]) -> None:
     """Raises one `WeightsMismatchError` that lists every difference."""
-    missing = sorted(n for n in expected if n not in have)
+    missing = sorted(n for n, spec in expected.items() if n not in have and not spec.optional)
     unexpected = sorted(n for n in have if n not in expected)
     wrong_shape, wrong_dtype = [], []
     for n, spec in expected.items():
@@ -137,4 +142,4 @@ def load_checked(model_dir: str, expected: Mapping[str, TensorSpec],
     src = WeightSource(model_dir, run_dtype)
     have = {n: (src.shape(n), src.stored_dtype(n)) for n in src.names()}
     check_against(model_dir, have, expected)
-    return {n: src.tensor(n) for n in expected}, src
+    return {n: src.tensor(n) for n in expected if n in have}, src

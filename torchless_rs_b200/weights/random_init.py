@@ -120,14 +120,14 @@ def _host_tensor(key: int, spec: TensorSpec, scale: float, shift: float, dtype: 
     if spec.integer:
         i = np.arange(n, dtype=np.uint64)
         v = ((_bits(key, i) >> np.uint64(32)) % np.uint64(INT_MODULUS)).astype(np.int32)
-        return torch.from_numpy(v).view(*spec.shape)
+        return torch.from_numpy(v).reshape(tuple(spec.shape))
     out = torch.empty(n, dtype=dtype)
     sc, sh = np.float32(scale), np.float32(shift)
     for a in range(0, n, _CHUNK):
         cnt = min(_CHUNK, n - a)
         z = standard_normals(key, a, cnt).astype(np.float32)
         out[a:a + cnt] = torch.from_numpy(z * sc + sh).to(dtype)
-    return out.view(*spec.shape)
+    return out.reshape(tuple(spec.shape))
 
 
 _lib = None
@@ -162,6 +162,8 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype,
     dev = torch.device(device)
     key = tensor_key(seed, name)
     scale, shift = (NORM_STD, 1.0) if len(spec.shape) == 1 else (MATRIX_STD, 0.0)
+    if spec.init is not None:
+        scale, shift = float(spec.init[0]), float(spec.init[1])
     if dev.type == "cuda" and (spec.integer or dtype in (torch.float32, torch.bfloat16)):
         return _device_tensor(key, spec, scale, shift, dtype, dev)
     return _host_tensor(key, spec, scale, shift, dtype).to(dev)
@@ -170,7 +172,8 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype,
 def random_tensors(expected: Mapping[str, TensorSpec], seed: int, dtype: torch.dtype,
                    device: str | torch.device = "cpu") -> Iterator[Tuple[str, torch.Tensor]]:
     for name, spec in expected.items():
-        yield name, random_tensor(name, spec, seed, dtype, device)
+        if not spec.optional:
+            yield name, random_tensor(name, spec, seed, dtype, device)
 
 
 def write_random_model(config, out_dir: str, seed: int, dtype: torch.dtype = torch.bfloat16,
