@@ -279,8 +279,65 @@ def reference_arm(args) -> int:
     return 0
 
 
+def design_arm(args) -> int:
+    """`--design kikopel`: prefill and decode throughput of the Kikopel design at layer sizes of a real
+    model (random weights), beside Mistral (the closest existing model) at equal width, heads, layers,
+    feed-forward and window, and every kernel of the design alone against its roofline beside the like
+    kernel of the Mistral path.  One JSON line; the default workload is not touched."""
+    import torch
+    import torchless_rs_b200 as tl
+    from torchless_rs_b200 import measure
+    from torchless_rs_b200.config import config_from_dict
+    from torchless_rs_b200.sampling.params import SamplingParams
+    size, L = args.design_size, args.layers or 8
+    T, B, ctx = PREFILL_TOKENS, args.batch or 8, 2048
+    out = {"design": "kikopel", "sizes": dict(measure.KIKOPEL_SIZES[size]), "layers": L, "dtype": "bf16",
+           "data": "synthetic: random weights, fixed token ids", "prefill_tokens": T, "decode_batch": B,
+           "decode_context": ctx, "steps": args.steps, "warmup": args.warmup}
+    clocks = ClockSampler()
+    clocks.start()
+    t0 = clocks.mark()
+    greedy = SamplingParams.greedy()
+    for name, cfg in (("kikopel", measure.kikopel_config(size, L)), ("mistral", measure.mistral_like(size, L))):
+        model = tl.from_random(config_from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=B * (ctx + 64),
+                               max_batch=B, max_seq_len=ctx + 64)
+        eng = model.engine
+        pre_ms, pre_all = prefill_timed(model, T, repeats=3)
+        # decode: every sequence is prefilled to the context first, then K steps are timed on the device
+        toks = [[(13 * i + 7 * b + 1) % eng.vocab_size for i in range(ctx - args.steps - args.warmup)] for b in range(B)]
+        slots = eng.start_sequences(B)
+        for b in range(B):
+            eng.prefill([slots[b]], [toks[b]])
+        one = [[(7 * i + 3) % eng.vocab_size] for i in range(B)]
+        for _ in range(args.warmup):
+            model.sampler.select(eng.step(slots, one, "last"), greedy)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            model.sampler.select(eng.step(slots, one, "last"), greedy)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        eng.end_sequences(slots)
+        eng.check_kernels()
+        out[name] = {"prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(T / (pre_ms / 1e3), 1),
+                     "prefill_ms_each": [round(t, 2) for t in pre_all], "decode_ms_per_step": round(ms, 4),
+                     "decode_tok_s": round(B / (ms / 1e3), 1), "weight_bytes": eng.model.weight_bytes()}
+        del model, eng
+        torch.cuda.empty_cache()
+    out["kernels"] = measure.kikopel_kernels(size, T, B, ctx, 24)
+    clocks.stop()
+    out["clocks"] = clocks.summary(t0, clocks.mark())
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default=None, choices=["kikopel"],
+                    help="measure another design beside Mistral at equal sizes instead of the default workload")
+    ap.add_argument("--design-size", default="1b", choices=["1b", "7b"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
@@ -294,6 +351,9 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        args.warmup = max(args.warmup, 3)
+        return design_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not measured")
         return 2

@@ -260,7 +260,7 @@ def test_latent_attention_sees_exactly_its_window(dtype, rank, rot, dims, heads,
                 q_t = np.zeros((T, heads * (3 + rot))); q_t[-1] = np.concatenate(
                     [np.concatenate([np.zeros(3), qr[h]]) for h in range(heads)])
                 out = torch.zeros((T, heads, rank), dtype=torch.float32).cuda()
-                o.latent_attn(_dev(qa_t), _dev(q_t), 3 + rot, 3, store, out, _i32(pos), _i32([0] * T), _i32([slot]),
+                o.latent_attn(_dev(qa_t.reshape(T, heads * rank)), rank, _dev(q_t), 3 + rot, 3, store, out, _i32(pos), _i32([0] * T), _i32([slot]),
                               _i32(table), _dev(inv_freq) if dims else None, heads, rank, rot, dims, window, 0.5)
                 got = out[-1].cpu().numpy()
                 tol = 2e-5 if dtype == torch.float32 else 2e-2

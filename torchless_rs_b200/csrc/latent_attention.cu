@@ -197,13 +197,35 @@ extern "C" int TL_NAME(tl_headwise_gemm)(const float* A, int lda, int a_head, co
 // from 0), taken 128 at a time from the first visible one with a running maximum and sum, so a
 // position's result is the same in whatever step or batch it is computed.  The weighted sum of
 // the rows' first `rank` numbers goes to o[t, h, :] (32-bit).
-//   qa  [T, heads, rank] 32-bit;  q [T, ldq] 32-bit, head h's rotated part at h * q_head + q_off
+//   qa [T, ld_qa] 32-bit, head h's latent-space query at h * qa_head;  q [T, ldq] 32-bit, head h's
+//   part to rotate at h * q_head + q_off (both may lie in one buffer)
 // ---------------------------------------------------------------------------
 #define LAT_THREADS 128
 #define LAT_MAX_PER_THREAD 8   // rank <= 1024
 
+#if TL_DTYPE == 0
+#define LVEC 4
+__device__ __forceinline__ void load_row_vec(const act_t* p, float* out) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+#else
+#define LVEC 8
+__device__ __forceinline__ void load_row_vec(const act_t* p, float* out) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+#endif
+
 __global__ void __launch_bounds__(LAT_THREADS)
-latent_attn_kernel(const float* __restrict__ qa, const float* __restrict__ q, int ldq, int q_head, int q_off,
+latent_attn_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, const float* __restrict__ q, int ldq,
+                   int q_head, int q_off,
                    const act_t* __restrict__ pages, float* __restrict__ o, const int* __restrict__ token_pos,
                    const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                    const int* __restrict__ page_table, int table_stride, const float* __restrict__ inv_freq,
@@ -219,7 +241,8 @@ latent_attn_kernel(const float* __restrict__ qa, const float* __restrict__ q, in
   const int pos = token_pos[t];
   const int* table = page_table + (size_t)seq_slot[token_seq[t]] * table_stride;
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  for (int i = tid; i < rank; i += LAT_THREADS) qs[i] = qa[((size_t)t * heads + h) * rank + i] * scale;
+  const bool vec = width % LVEC == 0;     // rows then start on 16-byte boundaries
+  for (int i = tid; i < rank; i += LAT_THREADS) qs[i] = qa[(size_t)t * ld_qa + (size_t)h * qa_head + i] * scale;
   {
     const float* r = q + (size_t)t * ldq + (size_t)h * q_head + q_off;
     const int half = dims >> 1;
@@ -246,7 +269,16 @@ latent_attn_kernel(const float* __restrict__ qa, const float* __restrict__ q, in
       page = table[i / TL_PAGE];
       const act_t* krow = pages + ((size_t)page * TL_PAGE + (i % TL_PAGE)) * width;
       float dot = 0.0f;
-      for (int d = 0; d < width; ++d) dot = fmaf(qs[d], to_f32(krow[d]), dot);
+      if (vec) {
+        for (int d = 0; d < width; d += LVEC) {
+          float kv[LVEC];
+          load_row_vec(krow + d, kv);
+#pragma unroll
+          for (int e = 0; e < LVEC; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+        }
+      } else {
+        for (int d = 0; d < width; ++d) dot = fmaf(qs[d], to_f32(krow[d]), dot);
+      }
       s = dot;
     }
     const float cmax = block_max(s, scratch);
@@ -281,7 +313,8 @@ latent_attn_kernel(const float* __restrict__ qa, const float* __restrict__ q, in
   }
 }
 
-extern "C" int TL_NAME(tl_latent_attn)(const float* qa, const float* q, int ldq, int q_head, int q_off,
+extern "C" int TL_NAME(tl_latent_attn)(const float* qa, int ld_qa, int qa_head, const float* q, int ldq,
+                                       int q_head, int q_off,
                                        const void* pages, float* o, const int* token_pos, const int* token_seq,
                                        const int* seq_slot, const int* page_table, int table_stride,
                                        const float* inv_freq, int T, int heads, int rank, int rot, int dims,
@@ -291,6 +324,6 @@ extern "C" int TL_NAME(tl_latent_attn)(const float* qa, const float* q, int ldq,
   if (rank > LAT_THREADS * LAT_MAX_PER_THREAD || heads > 65535 || (rank + rot) * sizeof(float) > 40 * 1024)
     return TL_ERR_UNSUPPORTED;
   return tl_launch(latent_attn_kernel, dim3(T, heads), dim3(LAT_THREADS), (size_t)(rank + rot) * sizeof(float),
-                   stream, qa, q, ldq, q_head, q_off, (const act_t*)pages, o, token_pos, token_seq, seq_slot,
+                   stream, qa, ld_qa, qa_head, q, ldq, q_head, q_off, (const act_t*)pages, o, token_pos, token_seq, seq_slot,
                    page_table, table_stride, inv_freq, heads, rank, rot, dims, window, scale);
 }

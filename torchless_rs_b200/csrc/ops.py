@@ -392,26 +392,28 @@ class CoreOps:
                                       c_int(K), c_int(heads), c_int(0 if gate is None else 1), _stream()),
                "headwise_gemm")
 
-    def latent_attn(self, qa: torch.Tensor, q: torch.Tensor, q_head: int, q_off: int, pages: torch.Tensor,
-                    out: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slot: torch.Tensor,
-                    page_table: torch.Tensor, inv_freq: Optional[torch.Tensor], heads: int, rank: int, rot: int,
-                    dims: int, window: Optional[int], scale: float) -> None:
+    def latent_attn(self, qa: torch.Tensor, qa_head: int, q: torch.Tensor, q_head: int, q_off: int,
+                    pages: torch.Tensor, out: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+                    seq_slot: torch.Tensor, page_table: torch.Tensor, inv_freq: Optional[torch.Tensor], heads: int,
+                    rank: int, rot: int, dims: int, window: Optional[int], scale: float) -> None:
         """out[t, h, :] = softmax over the visible positions of ((qa[t, h] . c + rotate(q_rot[t, h]) . r) *
-        scale) times the positions' c; page rows are [c | r]."""
-        _need(qa, torch.float32, "latent queries")
+        scale) times the positions' c; page rows are [c | r].  Head h's latent-space query starts at column
+        h * qa_head of `qa`, its part to rotate at column h * q_head + q_off of `q` (one buffer may be both)."""
+        _need(qa, torch.float32, "latent queries", contiguous=False)
         _need(q, torch.float32, "queries", contiguous=False)
         _need(pages, self.act_dtype, "latent pages")
         _need(out, torch.float32, "latent attention out")
         _need(page_table, torch.int32, "page table")
         T = qa.shape[0]
-        if qa.shape != (T, heads, rank) or out.shape != (T, heads, rank) or q.stride(1) != 1 or \
-                pages.shape[1:] != (PAGE, rank + rot) or q.shape[1] < (heads - 1) * q_head + q_off + rot:
+        if out.shape != (T, heads, rank) or q.stride(1) != 1 or qa.stride(1) != 1 or q.shape[0] != T or \
+                pages.shape[1:] != (PAGE, rank + rot) or q.shape[1] < (heads - 1) * q_head + q_off + rot or \
+                qa.shape[1] < (heads - 1) * qa_head + rank:
             raise KernelError("latent_attn: sizes do not match")
         _check(self._tl_latent_attn(
-            _ptr(qa), _ptr(q), c_int(q.stride(0)), c_int(q_head), c_int(q_off), _ptr(pages), _ptr(out),
-            _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)),
-            _ptr(inv_freq if dims else None), c_int(T), c_int(heads), c_int(rank), c_int(rot), c_int(dims),
-            c_int(window or 0), c_float(scale), _stream()), "latent_attn")
+            _ptr(qa), c_int(qa.stride(0)), c_int(qa_head), _ptr(q), c_int(q.stride(0)), c_int(q_head), c_int(q_off),
+            _ptr(pages), _ptr(out), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table),
+            c_int(page_table.stride(0)), _ptr(inv_freq if dims else None), c_int(T), c_int(heads), c_int(rank),
+            c_int(rot), c_int(dims), c_int(window or 0), c_float(scale), _stream()), "latent_attn")
 
     # ---- gated linear recurrence ------------------------------------------------------------------
     def gated_scan(self, z: torch.Tensor, bias: torch.Tensor, low: torch.Tensor, state: torch.Tensor,

@@ -170,6 +170,150 @@ MODEL_SIZES = {
 SIZES = MISTRAL_7B_SIZES   # what `step` and `timeline` build; --model chooses
 
 
+# Layer sizes at which the Kikopel kernels are measured: the width, heads and feed-forward of a 1B- and a
+# 7B-class decoder, latent ranks and head sizes as published latent-attention models have them, a recurrent
+# state of 128 x 128 per head.
+KIKOPEL_SIZES = {
+    "1b": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, window=4096, ff=5632,
+               r_heads=16, r_dim=128, r_vdim=128, vocab=32000),
+    "7b": dict(width=4096, heads=32, dim=128, rot=64, vdim=128, q_rank=1536, kv_rank=512, window=4096, ff=14336,
+               r_heads=32, r_dim=128, r_vdim=128, vocab=32000),
+}
+
+
+def kikopel_config(size: str, layers: int) -> dict:
+    """config.json of a Kikopel model of `layers` layers at these sizes: attention, recurrence, attention,
+    attention, and so on."""
+    z = KIKOPEL_SIZES[size]
+    att = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": z["ff"]},
+           "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"],
+                     "q_rank": z["q_rank"], "kv_rank": z["kv_rank"], "mask": {"size": z["window"]},
+                     "rot": {"base": 1e6, "dims": z["rot"]}, "scale": 1.0 / math.sqrt(z["dim"] + z["rot"])}}
+    rec = {"type": "hgrn2", "mlp": {"kind": "dense", "ff": z["ff"]},
+           "mixer": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"]}}
+    return {"architecture": "Kikopel", "width": z["width"], "vocab": z["vocab"], "norm": {"eps": 1e-5},
+            "residual_mult": 0.7, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+            "layers": [rec if i % 4 == 1 else att for i in range(layers)], "max_position_embeddings": 32768}
+
+
+def mistral_like(size: str, layers: int) -> dict:
+    """The closest existing model at equal size: Mistral with the same width, heads, feed-forward and window."""
+    z = KIKOPEL_SIZES[size]
+    return dict(MISTRAL_7B_SIZES, num_hidden_layers=layers, hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=max(1, z["heads"] // 4), head_dim=128, intermediate_size=z["ff"],
+                vocab_size=z["vocab"], sliding_window=z["window"], max_position_embeddings=32768)
+
+
+def kikopel_kernels(size: str, T: int, B: int, ctx: int, iters: int) -> list:
+    """Every kernel of the Kikopel design alone at the sizes `size`, for a prompt of T tokens and for a decode
+    step of B sequences at a context of `ctx`, beside the like kernel of the Mistral path at equal sizes.
+    Returns rows (name, case, microseconds, fraction of the roofline, what bounds it) and prints them.  The
+    roofline of a kernel is the larger of its algorithmic bytes over the measured copy bandwidth and its
+    FLOPs over the measured bf16 tensor rate (also for kernels that run on CUDA cores: the like kernels of
+    the Mistral path are on tensor cores, and the comparison is against what the hardware could do)."""
+    import json
+    import os
+    from .csrc import ops
+    from .csrc.attention_bf16 import AttentionBf16
+    z = KIKOPEL_SIZES[size]
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    pk = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.isfile(pk):
+        peaks.update(json.load(open(pk)))
+    o = ops.core_ops(torch.bfloat16)
+    dev, bf = "cuda", torch.bfloat16
+    H, rank, rot, vdim, W = z["heads"], z["kv_rank"], z["rot"], z["vdim"], z["width"]
+    width = rank + rot
+    rows = []
+
+    def report(name, case, us, byts, flops):
+        t_mem, t_fl = byts / (peaks["hbm_gbs"] * 1e3), flops / (peaks["bf16_tflops"] * 1e6)     # microseconds
+        frac = max(t_mem, t_fl) / us
+        rows.append({"kernel": name, "case": case, "us": round(us, 2), "roofline_frac": round(frac, 4),
+                     "bound": "memory" if t_mem >= t_fl else "tensor"})
+        print(f"{name:28s} {case:22s} {us:10.2f} us   {frac:7.4f} of the roofline ({rows[-1]['bound']})")
+
+    inv = torch.tensor([1e6 ** (-2.0 * i / rot) for i in range(rot // 2)], device=dev)
+    for case, n_tok, seqs, past in ((f"prompt {T}", T, 1, 0), (f"decode {B} x {ctx}", B, B, ctx - 1)):
+        per = n_tok // seqs
+        pages_per = (past + per + 63) // 64
+        pos = torch.cat([torch.arange(past, past + per, dtype=torch.int32) for _ in range(seqs)]).to(dev)
+        seq = torch.arange(seqs, dtype=torch.int32).repeat_interleave(per).to(dev)
+        slot = torch.arange(seqs, dtype=torch.int32, device=dev)
+        start = (torch.arange(seqs + 1, dtype=torch.int32) * per).to(dev)
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=dev).view(seqs, pages_per)
+        seen = sum(min(p + 1, z["window"]) for p in range(past, past + per)) * seqs      # (query, key) pairs
+        # --- the attention through latents, and Mistral's attention at equal heads
+        pages = torch.randn((seqs * pages_per, 64, width), device=dev, dtype=bf)
+        q = torch.randn((n_tok, H * width), device=dev) * 0.1
+        mix = torch.empty((n_tok, H, rank), device=dev)
+        us = _time(lambda: o.latent_attn(q, width, q, width, rank, pages, mix, pos, seq, slot, table, inv, H, rank,
+                                         rot, rot, z["window"], 0.04), max(2, iters // 8) if n_tok > 64 else iters)
+        cache_b = 2.0 * seqs * min(past + per, z["window"]) * width
+        report("latent_attn", case, us, cache_b + n_tok * H * (width + rank) * 4.0, 2.0 * H * seen * (width + rank))
+        nkv = max(1, H // 4)
+        att = AttentionBf16.get(128)
+        kp, vp, tab2, slot2 = _paged(seqs, past + per, nkv, 128)
+        qm = torch.randn((n_tok, H * 128), device=dev, dtype=bf)
+        om = torch.empty_like(qm)
+        lens = torch.full((seqs,), past + per, dtype=torch.int32, device=dev)
+        if seqs == 1:
+            us = _time(lambda: att.prefill(qm, kp, vp, om, start, lens, slot2, tab2, 1, n_tok, H, nkv, z["window"],
+                                           0.088, variant="tc"), iters)
+        else:
+            from .csrc import attention_bf16
+            from .parts.runtime import Workspace
+            ws = Workspace(torch.device("cuda"))
+            n = attention_bf16.decode_splits(seqs, nkv, past + per, z["window"])
+            us = _time(lambda: att.decode(qm, kp, vp, om, lens, slot2, tab2, H, nkv, z["window"], 0.088, n, ws), iters)
+        report("  like: attention (Mistral)", case, us,
+               2.0 * seqs * min(past + per, z["window"]) * nkv * 128 * 2 + n_tok * H * 128 * 4.0, 4.0 * H * 128 * seen)
+        # --- per-head value up-projection with the gate, beside a tensor-core product of the same FLOPs
+        wuv = torch.randn((H, vdim, rank), device=dev, dtype=bf) * 0.02
+        gate = torch.randn((n_tok, H * vdim), device=dev)
+        og = torch.empty((n_tok, H * vdim), device=dev, dtype=bf)
+        us = _time(lambda: o.headwise_gemm(mix.view(n_tok, H * rank), rank, wuv, og, vdim, gate=gate), iters)
+        report("headwise_gemm (values, gate)", case, us,
+               H * vdim * rank * 2.0 + n_tok * H * (rank * 4.0 + vdim * 6.0), 2.0 * n_tok * H * vdim * rank)
+        # --- what is written per token, beside Mistral's rotation + cache write
+        dq = torch.randn((n_tok, z["q_rank"] + width), device=dev)
+        cq = torch.empty((n_tok, z["q_rank"]), device=dev, dtype=bf)
+        wq, wc = torch.ones(z["q_rank"], device=dev), torch.ones(rank, device=dev)
+        us = _time(lambda: o.latent_prep(dq[:, :z["q_rank"]], dq[:, z["q_rank"]:], wq, wc, 1e-5, cq, pages, pos, seq,
+                                         slot, table, inv, rank, rot, rot), iters)
+        report("latent_prep", case, us, n_tok * ((z["q_rank"] + width) * 4.0 + (z["q_rank"] + width) * 2.0), 0.0)
+        qkv = torch.randn((n_tok, (H + 2 * nkv) * 128), device=dev)
+        inv128 = torch.tensor([1e6 ** (-i / 64.0) for i in range(64)], device=dev)
+        us = _time(lambda: o.rope_cache_write(qkv, qm, kp, vp, pos, seq, slot2, tab2, inv128, 0, H, nkv, 128), iters)
+        report("  like: rope_cache_write", case, us, n_tok * (H + 2 * nkv) * 128 * 6.0, 0.0)
+        # --- the recurrence (no like kernel: the nearest is decode attention, which also streams per-sequence
+        # memory; its algorithmic bytes are the projections and, once per sequence, the state in and out)
+        rh, rd, rv = z["r_heads"], z["r_dim"], z["r_vdim"]
+        zz = torch.randn((n_tok, 2 * rh * rd + rh * rv), device=dev)
+        state = torch.zeros((seqs, rh, rd, rv), device=dev)
+        so = torch.empty((n_tok, rh * rv), device=dev)
+        bias, low = torch.zeros(rh * rd, device=dev), torch.full((rh * rd,), 0.5, device=dev)
+        us = _time(lambda: o.gated_scan(zz, bias, low, state, so, start, slot, rh, rd, rv),
+                   max(2, iters // 8) if n_tok > 64 else iters)
+        report("gated_scan", case, us, n_tok * (2 * rh * rd + 2 * rh * rv) * 4.0 + seqs * rh * rd * rv * 8.0,
+               4.0 * n_tok * rh * rd * rv)
+        # --- the branch's norm + residual sum and the activation, beside Mistral's norm kernel
+        y, x = torch.randn((n_tok, W), device=dev), torch.randn((n_tok, W), device=dev)
+        xb = torch.empty((n_tok, W), device=dev, dtype=bf)
+        g1 = torch.ones(1, device=dev)
+        us = _time(lambda: o.branch_norm_add(y, g1, 0.7, 1e-5, x, xb), iters)
+        report("branch_norm_add", case, us, n_tok * W * 14.0, 0.0)
+        zf = torch.randn((n_tok, z["ff"]), device=dev)
+        af = torch.empty((n_tok, z["ff"]), device=dev, dtype=bf)
+        co = torch.tensor([0.5, 0.3, 0.2, 0.1], device=dev)
+        us = _time(lambda: o.poly_norm(zf, co, 1e-5, af), iters)
+        report("poly_norm", case, us, n_tok * z["ff"] * 6.0, 0.0)
+        wn = torch.ones(W, device=dev, dtype=bf)
+        us = _time(lambda: o.rmsnorm(x, wn, 1e-5, xb), iters)
+        report("  like: rmsnorm", case, us, n_tok * W * 6.0, 0.0)
+    return rows
+
+
 def step(B: int, context: int, prefill: int, layers: int, iters: int) -> None:
     from . import from_random
     from .config import config_from_dict
@@ -331,12 +475,15 @@ def timeline(B: int, context: int, layers: int) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "step", "timeline", "decode"])
+    ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "step", "timeline", "decode",
+                                     "kikopel-kernels"])
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
     ap.add_argument("--model", default="mistral7b", choices=sorted(MODEL_SIZES),
                     help="step, timeline: whose layer sizes the model has")
+    ap.add_argument("--kikopel-size", default="1b", choices=sorted(KIKOPEL_SIZES),
+                    help="kikopel-kernels TOKENS BATCH CONTEXT: whose layer sizes the kernels get")
     ap.add_argument("--window", type=int, default=0, help="decode: the sliding window (0: none)")
     ap.add_argument("--equal-shares", action="store_true",
                     help="decode: every sequence's keys in equal shares (no page quantum)")
@@ -348,7 +495,9 @@ def main() -> None:
     if a.splits:
         from .csrc import attention_bf16
         attention_bf16.decode_splits = lambda *args, **kw: a.splits
-    if a.what == "gemm":
+    if a.what == "kikopel-kernels":
+        kikopel_kernels(a.kikopel_size, a.sizes[0], a.sizes[1], a.sizes[2], a.iters)
+    elif a.what == "gemm":
         gemm(*a.sizes[:4], a.iters)
     elif a.what == "elementwise":
         elementwise(a.sizes[0], min(a.iters, 24))

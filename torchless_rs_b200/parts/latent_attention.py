@@ -36,6 +36,7 @@ class LatentAttention:
     Tensors under the prefix: dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o."""
     graph_safe = True
     can_overwrite = True
+    FEW_TOKENS = 16     # up to here a step keeps W_uq and W_uk apart
 
     def __init__(self, spec: PartSpec, prefix: str, rt: Runtime, position=None):
         p = spec.params
@@ -89,6 +90,15 @@ class LatentAttention:
         self.w_uk_t = rt.matrix(uk)                                          # [heads, rank, dim]
         self.w_uv = rt.matrix(weights[f"{p}.uv"].reshape(self.heads, self.vdim, self.rank))
         self.w_o = rt.matrix(weights[f"{p}.o"])
+        # For steps of many tokens W_uk,h^T is folded into W_uq: one product gives every head's
+        # [latent-space query | part to rotate].  (Folded in 64-bit, once, when the weights come in.)
+        uq64 = weights[f"{p}.uq"].to(device=rt.device, dtype=torch.float64).reshape(
+            self.heads, self.dim + self.rot, self.q_rank)
+        uk64 = weights[f"{p}.uk"].to(device=rt.device, dtype=torch.float64).reshape(self.heads, self.dim, self.rank)
+        folded = torch.cat([torch.bmm(uk64.transpose(1, 2), uq64[:, :self.dim]), uq64[:, self.dim:]], dim=1)
+        self.w_q_latent = rt.matrix(folded.reshape(self.heads * (self.rank + self.rot), self.q_rank)
+                                    .to(torch.float32 if rt.is_f32 else torch.bfloat16))
+        del uq64, uk64, folded
         f32 = lambda t: t.to(device=rt.device, dtype=torch.float32).contiguous()
         self.norm_q = f32(weights[f"{p}.dq.norm"])
         self.norm_c = f32(weights[f"{p}.dkv.norm"])
@@ -112,13 +122,20 @@ class LatentAttention:
         o.latent_prep(s[:, :q_rank], s[:, q_rank:q_rank + rank + rot], self.norm_q, self.norm_c, self.eps, cq,
                       c.pages, batch.token_pos, batch.token_seq, batch.seq_slot, c.page_table, inv_freq,
                       rank, rot, self.rot_dims)
-        q = ws.get("latent_q", (T, H * (dim + rot)), torch.float32)
-        self.matmul(cq, self.w_uq, q, ops.MODE_STORE_F32)
-        qa = ws.get("latent_qa", (T, H, rank), torch.float32)
-        o.headwise_gemm(q, dim + rot, self.w_uk_t, qa.view(T, H * rank), rank)
         mix = ws.get("latent_mix", (T, H, rank), torch.float32)
-        o.latent_attn(qa, q, dim + rot, dim, c.pages, mix, batch.token_pos, batch.token_seq, batch.seq_slot,
-                      c.page_table, inv_freq, H, rank, rot, self.rot_dims, self.window, self.scale)
+        if T <= self.FEW_TOKENS:
+            # few tokens: the two small matrices are fewer bytes to stream than the folded one
+            q = ws.get("latent_q", (T, H * (dim + rot)), torch.float32)
+            self.matmul(cq, self.w_uq, q, ops.MODE_STORE_F32)
+            qa = ws.get("latent_qa", (T, H * rank), torch.float32)
+            o.headwise_gemm(q, dim + rot, self.w_uk_t, qa, rank)
+            o.latent_attn(qa, rank, q, dim + rot, dim, c.pages, mix, batch.token_pos, batch.token_seq,
+                          batch.seq_slot, c.page_table, inv_freq, H, rank, rot, self.rot_dims, self.window, self.scale)
+        else:
+            q = ws.get("latent_ql", (T, H * (rank + rot)), torch.float32)
+            self.matmul(cq, self.w_q_latent, q, ops.MODE_STORE_F32)
+            o.latent_attn(q, rank + rot, q, rank + rot, rank, c.pages, mix, batch.token_pos, batch.token_seq,
+                          batch.seq_slot, c.page_table, inv_freq, H, rank, rot, self.rot_dims, self.window, self.scale)
         gated = ws.get("latent_gated", (T, H * vdim), rt.act_dtype)
         o.headwise_gemm(mix.view(T, H * rank), rank, self.w_uv, gated, vdim, gate=s[:, q_rank + rank + rot:])
         self.matmul(gated, self.w_o, residual, ops.MODE_STORE_F32 if overwrite else ops.MODE_ACCUM_F32)
