@@ -133,6 +133,7 @@ extern "C" int TL_NAME(tl_branch_norm_add)(const float* y, int ldy, const float*
 // out[r, :] = a N(z) + b N(z^2) + c N(z^3) + e over a row z of F numbers, powers taken element by
 // element, N(u) = u / sqrt(mean(u^2) + eps); coeff = (a, b, c, e).  z 32-bit with row stride ldz.
 // ---------------------------------------------------------------------------
+#define POLY_KEEP 24
 __global__ void poly_norm_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ coeff,
                                  float eps, act_t* __restrict__ out, int F) {
   __shared__ float scratch[33];
@@ -140,21 +141,47 @@ __global__ void poly_norm_kernel(const float* __restrict__ z, int ldz, const flo
   pdl_launch_dependents();
   const int r = blockIdx.x;
   const float* zr = z + (size_t)r * ldz;
+  // the row is read once and kept in registers if it fits, else read a second time
+  const bool fits = F <= (int)blockDim.x * POLY_KEEP;
+  float keep[POLY_KEEP];
   float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
-  for (int i = threadIdx.x; i < F; i += blockDim.x) {
-    const float v = zr[i], v2 = v * v, v3 = v2 * v;
-    s2 = fmaf(v, v, s2);
-    s4 = fmaf(v2, v2, s4);
-    s6 = fmaf(v3, v3, s6);
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < POLY_KEEP; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      const float v = i < F ? zr[i] : 0.0f, v2 = v * v, v3 = v2 * v;
+      keep[j] = v;
+      s2 = fmaf(v, v, s2);
+      s4 = fmaf(v2, v2, s4);
+      s6 = fmaf(v3, v3, s6);
+    }
+  } else {
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+      const float v = zr[i], v2 = v * v, v3 = v2 * v;
+      s2 = fmaf(v, v, s2);
+      s4 = fmaf(v2, v2, s4);
+      s6 = fmaf(v3, v3, s6);
+    }
   }
   s2 = block_sum(s2, scratch);
   s4 = block_sum(s4, scratch);
   s6 = block_sum(s6, scratch);
   const float r1 = sqrtf(s2 / (float)F + eps), r2 = sqrtf(s4 / (float)F + eps), r3 = sqrtf(s6 / (float)F + eps);
   const float a = coeff[0], b = coeff[1], c = coeff[2], e = coeff[3];
-  for (int i = threadIdx.x; i < F; i += blockDim.x) {
-    const float v = zr[i], v2 = v * v, v3 = v2 * v;
-    out[(size_t)r * F + i] = from_f32<act_t>(a * (v / r1) + b * (v2 / r2) + c * (v3 / r3) + e);
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < POLY_KEEP; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < F) {
+        const float v = keep[j], v2 = v * v, v3 = v2 * v;
+        out[(size_t)r * F + i] = from_f32<act_t>(a * (v / r1) + b * (v2 / r2) + c * (v3 / r3) + e);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+      const float v = zr[i], v2 = v * v, v3 = v2 * v;
+      out[(size_t)r * F + i] = from_f32<act_t>(a * (v / r1) + b * (v2 / r2) + c * (v3 / r3) + e);
+    }
   }
 }
 
@@ -162,6 +189,6 @@ extern "C" int TL_NAME(tl_poly_norm)(const float* z, int ldz, const float* coeff
                                      int F, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (F <= 0 || coeff == nullptr) return TL_ERR_BAD_ARG;
-  const int threads = F <= 1024 ? 128 : F <= 8192 ? 256 : 512;
+  const int threads = F <= 2048 ? 128 : F <= 6144 ? 256 : 512;
   return tl_launch(poly_norm_kernel, dim3(rows), dim3(threads), 0, stream, z, ldz, coeff, eps, (act_t*)out, F);
 }

@@ -327,3 +327,325 @@ extern "C" int TL_NAME(tl_latent_attn)(const float* qa, int ld_qa, int qa_head, 
                    stream, qa, ld_qa, qa_head, q, ldq, q_head, q_off, (const act_t*)pages, o, token_pos, token_seq, seq_slot,
                    page_table, table_stride, inv_freq, heads, rank, rot, dims, window, scale);
 }
+
+#if TL_DTYPE == 1
+// ---------------------------------------------------------------------------
+// The same attention on tensor cores (bfloat16 build).  All heads of a token share the keys, so
+// the heads are the rows of the tiles: a block takes one token and up to 16 heads, and a part of
+// the token's visible keys (`splits` parts; more than one for decode steps, whose few tokens
+// would leave most of the GPU idle; a second kernel merges the parts).
+//
+// Per chunk of 64 keys: the chunk's page rows are copied to shared memory once (cp.async) and
+// serve both products.  Scores: each of the 4 warps takes 16 keys, S[16 heads x 16 keys] =
+// Q K^T by mma.sync m16n8k16 (Q, rotated and scaled, lies in shared memory as bfloat16), and
+// writes them in 32-bit to shared memory.  Softmax: every warp reads all 64 scores of its rows
+// in the layout of an A operand, keeps the running maximum and sum in 32-bit (the same numbers in
+// every warp), and rounds the weights to bfloat16.  Weighted sum: the warps share the columns of c
+// in groups of 16; B operands are read from the same rows with ldmatrix.trans; the sums stay in
+// registers (32-bit) over all chunks.
+// Needs rank and rot to be multiples of 16 and rank <= 512; other sizes take the kernel above.
+// ---------------------------------------------------------------------------
+#define LM_KC 64
+#define LM_THREADS 128
+#define LM_SPITCH (LM_KC + 4)
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+               "{%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// NTP: pairs of 8-column tiles of c per warp (rank <= 64 * NTP).
+template <int NTP>
+__global__ void __launch_bounds__(LM_THREADS)
+latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, const float* __restrict__ q, int ldq,
+                       int q_head, int q_off, const __nv_bfloat16* __restrict__ pages, float* __restrict__ o,
+                       float* __restrict__ part, const int* __restrict__ token_pos,
+                       const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                       const int* __restrict__ page_table, int table_stride, const float* __restrict__ inv_freq,
+                       int heads, int rank, int rot, int dims, int window, float scale, int splits) {
+  extern __shared__ __align__(16) unsigned char lm_smem[];
+  const int width = rank + rot, pitch = width + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lm_smem);          // [16][pitch]
+  __nv_bfloat16* Ks = Qs + 16 * pitch;                                     // [LM_KC][pitch]
+  float* Ss = reinterpret_cast<float*>(Ks + LM_KC * pitch);                // [16][LM_SPITCH]
+  const __nv_bfloat16** rowp = reinterpret_cast<const __nv_bfloat16**>(Ss + 16 * LM_SPITCH);   // [LM_KC]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, split = blockIdx.y, hg = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, qd = lane & 3;
+  const int pos = token_pos[t];
+  const int* table = page_table + (size_t)seq_slot[token_seq[t]] * table_stride;
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int n_chunks = (pos - lo + LM_KC) / LM_KC;
+  const int per_split = (n_chunks + splits - 1) / splits;
+  const int c_begin = split * per_split;
+  const int c_end = min(n_chunks, c_begin + per_split);
+  // the queries of this block's heads: [latent-space part | rotated part], times scale
+  {
+    const int half = dims >> 1;
+    for (int idx = tid; idx < 16 * width; idx += LM_THREADS) {
+      const int r = idx / width, d = idx - r * width, h = hg * 16 + r;
+      float v = 0.0f;
+      if (h < heads) {
+        if (d < rank) {
+          v = qa[(size_t)t * ld_qa + (size_t)h * qa_head + d];
+        } else {
+          const float* src = q + (size_t)t * ldq + (size_t)h * q_head + q_off;
+          const int j = d - rank;
+          if (j < dims) {
+            const int i = j < half ? j : j - half;
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float u = src[i], w = src[i + half];
+            v = j < half ? u * cs - w * sn : w * cs + u * sn;
+          } else {
+            v = src[j];
+          }
+        }
+        v *= scale;
+      }
+      Qs[r * pitch + d] = __float2bfloat16_rn(v);
+    }
+  }
+  float acc[2 * NTP][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NTP; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};   // rows g and g + 8
+  const int n_pairs = rank >> 4;        // groups of 16 columns of c
+  const int vecs = width >> 3;          // 16-byte pieces per row
+  for (int c = c_begin; c < c_end; ++c) {
+    const int base = lo + c * LM_KC;
+    __syncthreads();     // the chunk before is done with Ks, Ss and rowp (and Qs is written)
+    if (tid < LM_KC) {
+      const int i = base + tid;
+      rowp[tid] = i <= pos ? pages + ((size_t)table[i / TL_PAGE] * TL_PAGE + (i % TL_PAGE)) * width : nullptr;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < LM_KC * vecs; idx += LM_THREADS) {
+      const int r = idx / vecs, v = idx - r * vecs;
+      __nv_bfloat16* dst = Ks + r * pitch + v * 8;
+      if (rowp[r] != nullptr) {
+        const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(rowp[r] + v * 8) : "memory");
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    // scores of this warp's 16 keys
+    float sc[2][4] = {};
+    {
+      const __nv_bfloat16* qrow = Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (lane >> 4) * 8;
+      const __nv_bfloat16* krow = Ks + (warp * 16 + (lane >> 4) * 8 + (lane & 7)) * pitch + ((lane >> 3) & 1) * 8;
+      for (int ks = 0; ks < width; ks += 16) {
+        uint32_t a[4], b[4];
+        ldsm_x4(a, qrow + ks);
+        ldsm_x4(b, krow + ks);
+        mma_bf16(sc[0], a, b[0], b[1]);
+        mma_bf16(sc[1], a, b[2], b[3]);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int col = warp * 16 + nt * 8 + qd * 2;
+      const bool v0 = base + col <= pos, v1 = base + col + 1 <= pos;
+      Ss[g * LM_SPITCH + col] = v0 ? sc[nt][0] : -INFINITY;
+      Ss[g * LM_SPITCH + col + 1] = v1 ? sc[nt][1] : -INFINITY;
+      Ss[(g + 8) * LM_SPITCH + col] = v0 ? sc[nt][2] : -INFINITY;
+      Ss[(g + 8) * LM_SPITCH + col + 1] = v1 ? sc[nt][3] : -INFINITY;
+    }
+    __syncthreads();
+    // softmax over the chunk, per row; the weights as A operands of the second product
+    float s[2][LM_KC / 16][4];
+    float cmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int kk = 0; kk < LM_KC / 16; ++kk) {
+        const float2 x = *reinterpret_cast<const float2*>(Ss + (g + 8 * r) * LM_SPITCH + kk * 16 + qd * 2);
+        const float2 y = *reinterpret_cast<const float2*>(Ss + (g + 8 * r) * LM_SPITCH + kk * 16 + 8 + qd * 2);
+        s[r][kk][0] = x.x; s[r][kk][1] = x.y; s[r][kk][2] = y.x; s[r][kk][3] = y.y;
+        cmax[r] = fmaxf(cmax[r], fmaxf(fmaxf(x.x, x.y), fmaxf(y.x, y.y)));
+      }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      cmax[r] = fmaxf(cmax[r], __shfl_xor_sync(0xffffffffu, cmax[r], 1));
+      cmax[r] = fmaxf(cmax[r], __shfl_xor_sync(0xffffffffu, cmax[r], 2));
+      const float m_new = fmaxf(m_run[r], cmax[r]);      // finite: a chunk holds at least one visible key
+      alpha[r] = expf(m_run[r] - m_new);                 // 0 at the first chunk
+      float sum = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < LM_KC / 16; ++kk)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[r][kk][e] = expf(s[r][kk][e] - m_new);       // exp(-inf) = 0 for keys beyond the position
+          sum += s[r][kk][e];
+        }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l_run[r] = l_run[r] * alpha[r] + sum;
+      m_run[r] = m_new;
+    }
+#pragma unroll
+    for (int i = 0; i < 2 * NTP; ++i) {
+      acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];
+      acc[i][2] *= alpha[1]; acc[i][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < LM_KC / 16; ++kk) {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[0][kk][0], s[0][kk][1]);
+      a[1] = pack_bf16(s[1][kk][0], s[1][kk][1]);
+      a[2] = pack_bf16(s[0][kk][2], s[0][kk][3]);
+      a[3] = pack_bf16(s[1][kk][2], s[1][kk][3]);
+      const __nv_bfloat16* vrow = Ks + (kk * 16 + (lane & 15)) * pitch + (lane >> 4) * 8;
+#pragma unroll
+      for (int i = 0; i < NTP; ++i) {
+        const int pair = warp + 4 * i;
+        if (pair < n_pairs) {
+          uint32_t b[4];
+          ldsm_x4_trans(b, vrow + pair * 16);
+          mma_bf16(acc[2 * i], a, b[0], b[1]);
+          mma_bf16(acc[2 * i + 1], a, b[2], b[3]);
+        }
+      }
+    }
+  }
+  // out: normalised if this block saw all the keys, else this part's sums with its maximum and sum
+  const int hpad = gridDim.z * 16;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = hg * 16 + g + 8 * r;
+    if (splits == 1) {
+      if (row >= heads) continue;
+      const float inv = 1.0f / l_run[r];
+      float* dst = o + ((size_t)t * heads + row) * rank;
+#pragma unroll
+      for (int i = 0; i < NTP; ++i) {
+        const int pair = warp + 4 * i;
+        if (pair < n_pairs) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            *reinterpret_cast<float2*>(dst + pair * 16 + j * 8 + qd * 2) =
+                make_float2(acc[2 * i + j][2 * r] * inv, acc[2 * i + j][2 * r + 1] * inv);
+        }
+      }
+    } else {
+      float* dst = part + (((size_t)t * hpad + row) * splits + split) * (size_t)(rank + 2);
+#pragma unroll
+      for (int i = 0; i < NTP; ++i) {
+        const int pair = warp + 4 * i;
+        if (pair < n_pairs) {
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            *reinterpret_cast<float2*>(dst + pair * 16 + j * 8 + qd * 2) =
+                make_float2(acc[2 * i + j][2 * r], acc[2 * i + j][2 * r + 1]);
+        }
+      }
+      if (warp == 0 && qd == 0) { dst[rank] = m_run[r]; dst[rank + 1] = l_run[r]; }
+    }
+  }
+}
+
+// Merges the parts of a token's keys: out = sum_s w_s O_s / sum_s w_s l_s with w_s = exp(m_s - max m).
+__global__ void latent_attn_merge_kernel(const float* __restrict__ part, float* __restrict__ o, int heads, int hpad,
+                                         int rank, int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* src = part + ((size_t)t * hpad + h) * splits * (size_t)(rank + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, src[(size_t)s * (rank + 2) + rank]);
+  float l = 0.0f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = src[(size_t)s * (rank + 2) + rank];
+    if (ms != -INFINITY) l += expf(ms - m) * src[(size_t)s * (rank + 2) + rank + 1];
+  }
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float a = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = src[(size_t)s * (rank + 2) + rank];
+      if (ms != -INFINITY) a = fmaf(expf(ms - m), src[(size_t)s * (rank + 2) + d], a);
+    }
+    o[((size_t)t * heads + h) * rank + d] = a / l;
+  }
+}
+
+// How many parts the keys of a step's tokens are cut into, and how many floats the parts need.
+// `max_keys`: an upper bound of the keys any token of the step sees.
+extern "C" int tl_latent_attn_plan(int T, int heads, int rank, int rot, int max_keys, int num_sms,
+                                   long long* part_floats) {
+  *part_floats = 0;
+  if (rank % 16 || rot % 16 || rank > 512 || rank <= 0) return 0;     // the CUDA-core kernel
+  const size_t smem = (size_t)(16 + LM_KC) * (rank + rot + 8) * 2 + 16 * LM_SPITCH * 4 + LM_KC * 8;
+  if (smem > 200 * 1024) return 0;
+  const int groups = (heads + 15) / 16;
+  const long long blocks = (long long)T * groups;
+  int splits = 1;
+  const int chunks = (max_keys + LM_KC - 1) / LM_KC;
+  if (blocks < 2LL * num_sms) {
+    splits = (int)((2LL * num_sms + blocks - 1) / blocks);
+    if (splits > chunks) splits = chunks;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+  }
+  if (splits > 1) *part_floats = (long long)T * groups * 16 * splits * (rank + 2);
+  return splits;
+}
+
+extern "C" int tl_latent_attn_mma(const float* qa, int ld_qa, int qa_head, const float* q, int ldq, int q_head,
+                                  int q_off, const void* pages, float* o, float* part, const int* token_pos,
+                                  const int* token_seq, const int* seq_slot, const int* page_table,
+                                  int table_stride, const float* inv_freq, int T, int heads, int rank, int rot,
+                                  int dims, int window, float scale, int splits, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (rank % 16 || rot % 16 || rank > 512 || rank <= 0 || dims > rot || (dims & 1) || splits < 1 ||
+      (splits > 1 && part == nullptr))
+    return TL_ERR_UNSUPPORTED;
+  const int groups = (heads + 15) / 16;
+  if (splits > 65535 || groups > 65535) return TL_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)(16 + LM_KC) * (rank + rot + 8) * 2 + 16 * LM_SPITCH * 4 + LM_KC * 8;
+  dim3 grid(T, splits, groups);
+  int rc;
+#define LM_LAUNCH(NTP)                                                                                      \
+  {                                                                                                         \
+    static bool set = false;                                                                                \
+    if (!set) {                                                                                             \
+      if (cudaFuncSetAttribute(latent_attn_mma_kernel<NTP>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                               200 * 1024) != cudaSuccess)                                                  \
+        return TL_ERR_UNSUPPORTED;                                                                          \
+      set = true;                                                                                           \
+    }                                                                                                       \
+    rc = tl_launch(latent_attn_mma_kernel<NTP>, grid, dim3(LM_THREADS), smem, stream, qa, ld_qa, qa_head, q, \
+                   ldq, q_head, q_off, (const __nv_bfloat16*)pages, o, part, token_pos, token_seq, seq_slot, \
+                   page_table, table_stride, inv_freq, heads, rank, rot, dims, window, scale, splits);       \
+  }
+  if (rank <= 64) LM_LAUNCH(1)
+  else if (rank <= 128) LM_LAUNCH(2)
+  else if (rank <= 256) LM_LAUNCH(4)
+  else LM_LAUNCH(8)
+#undef LM_LAUNCH
+  if (rc != 0 || splits == 1) return rc;
+  return tl_launch(latent_attn_merge_kernel, dim3(T, heads), dim3(128), 0, stream, (const float*)part, o, heads,
+                   groups * 16, rank, splits);
+}
+#endif

@@ -42,37 +42,59 @@ gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, co
     for (int c = 0; c < SCAN_COLS; ++c)
       s[r][c] = (i < dim && c0 + c < vdim) ? S[(size_t)i * vdim + c0 + c] : 0.0f;
   }
-  for (int t = t0; t < t1; ++t) {
-    const float* rq = zq + (size_t)t * ld + h * dim;
-    const float* rf = zf + (size_t)t * ld + h * dim;
-    const float* rv = zv + (size_t)t * ld + h * vdim + c0;
-    float v[SCAN_COLS], part[SCAN_COLS];
+  // Tokens are taken PF at a time: their inputs are loaded and their gates computed together (all
+  // independent, so the loads are in flight at once), then the state walks through them in order.
+  constexpr int PF = R <= 4 ? 8 : 4;
+  for (int tb = t0; tb < t1; tb += PF) {
+    float qv[PF][R], fv[PF][R], vv[PF][SCAN_COLS];
 #pragma unroll
-    for (int c = 0; c < SCAN_COLS; ++c) {
-      v[c] = c0 + c < vdim ? rv[c] : 0.0f;
-      part[c] = 0.0f;
+    for (int p = 0; p < PF; ++p) {
+      const int t = tb + p < t1 ? tb + p : t1 - 1;
+      const float* rq = zq + (size_t)t * ld + h * dim;
+      const float* rf = zf + (size_t)t * ld + h * dim;
+      const float* rv = zv + (size_t)t * ld + h * vdim + c0;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int i = lane + 32 * r;
+        qv[p][r] = i < dim ? rq[i] : 0.0f;
+        fv[p][r] = i < dim ? rf[i] : 0.0f;
+      }
+#pragma unroll
+      for (int c = 0; c < SCAN_COLS; ++c) vv[p][c] = c0 + c < vdim ? rv[c] : 0.0f;
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int i = lane + 32 * r;
-      if (i < dim) {
-        const float z = rq[i];
-        const float qv = z / (1.0f + expf(-z));
-        const float f = lo[r] + (1.0f - lo[r]) * (1.0f / (1.0f + expf(-(rf[i] + bi[r]))));
-        const float w = 1.0f - f;
+    for (int p = 0; p < PF; ++p)
 #pragma unroll
-        for (int c = 0; c < SCAN_COLS; ++c) {
-          s[r][c] = fmaf(f, s[r][c], w * v[c]);
-          part[c] = fmaf(s[r][c], qv, part[c]);
+      for (int r = 0; r < R; ++r) {
+        const float z = qv[p][r];
+        qv[p][r] = z / (1.0f + expf(-z));
+        fv[p][r] = lo[r] + (1.0f - lo[r]) * (1.0f / (1.0f + expf(-(fv[p][r] + bi[r]))));
+      }
+#pragma unroll
+    for (int p = 0; p < PF; ++p) {
+      if (tb + p < t1) {
+        float part[SCAN_COLS];
+#pragma unroll
+        for (int c = 0; c < SCAN_COLS; ++c) part[c] = 0.0f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          if (lane + 32 * r < dim) {
+            const float f = fv[p][r], w = 1.0f - f;
+#pragma unroll
+            for (int c = 0; c < SCAN_COLS; ++c) {
+              s[r][c] = fmaf(f, s[r][c], w * vv[p][c]);
+              part[c] = fmaf(s[r][c], qv[p][r], part[c]);
+            }
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < SCAN_COLS; ++c) part[c] = warp_sum(part[c]);
+        if (lane == 0) {
+#pragma unroll
+          for (int c = 0; c < SCAN_COLS; ++c)
+            if (c0 + c < vdim) o[(size_t)(tb + p) * ldo + h * vdim + c0 + c] = part[c];
         }
       }
-    }
-#pragma unroll
-    for (int c = 0; c < SCAN_COLS; ++c) part[c] = warp_sum(part[c]);
-    if (lane == 0) {
-#pragma unroll
-      for (int c = 0; c < SCAN_COLS; ++c)
-        if (c0 + c < vdim) o[(size_t)t * ldo + h * vdim + c0 + c] = part[c];
     }
   }
 #pragma unroll

@@ -85,6 +85,16 @@ def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+_sms: Dict[int, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    i = device.index if device.index is not None else torch.cuda.current_device()
+    if i not in _sms:
+        _sms[i] = torch.cuda.get_device_properties(i).multi_processor_count
+    return _sms[i]
+
+
 def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
     if t is None:
         return c_void_p(0)
@@ -395,10 +405,15 @@ class CoreOps:
     def latent_attn(self, qa: torch.Tensor, qa_head: int, q: torch.Tensor, q_head: int, q_off: int,
                     pages: torch.Tensor, out: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
                     seq_slot: torch.Tensor, page_table: torch.Tensor, inv_freq: Optional[torch.Tensor], heads: int,
-                    rank: int, rot: int, dims: int, window: Optional[int], scale: float) -> None:
+                    rank: int, rot: int, dims: int, window: Optional[int], scale: float,
+                    max_keys: Optional[int] = None, workspace=None) -> None:
         """out[t, h, :] = softmax over the visible positions of ((qa[t, h] . c + rotate(q_rot[t, h]) . r) *
         scale) times the positions' c; page rows are [c | r].  Head h's latent-space query starts at column
-        h * qa_head of `qa`, its part to rotate at column h * q_head + q_off of `q` (one buffer may be both)."""
+        h * qa_head of `qa`, its part to rotate at column h * q_head + q_off of `q` (one buffer may be both).
+
+        In bfloat16 the tensor-core kernel runs where the sizes allow it (rank and rot multiples of 16,
+        rank <= 512); `max_keys` (an upper bound of the keys a token of the step sees) lets it cut the keys
+        of a step of few tokens into parts, whose partial sums lie in a buffer of `workspace`."""
         _need(qa, torch.float32, "latent queries", contiguous=False)
         _need(q, torch.float32, "queries", contiguous=False)
         _need(pages, self.act_dtype, "latent pages")
@@ -409,6 +424,27 @@ class CoreOps:
                 pages.shape[1:] != (PAGE, rank + rot) or q.shape[1] < (heads - 1) * q_head + q_off + rot or \
                 qa.shape[1] < (heads - 1) * qa_head + rank:
             raise KernelError("latent_attn: sizes do not match")
+        if self.act_dtype == torch.bfloat16:
+            from ctypes import byref, c_longlong
+            n = c_longlong(0)
+            bound = min(int(max_keys), int(window)) if (max_keys and window) else int(max_keys or window or (1 << 30))
+            splits = self.lib.tl_latent_attn_plan(c_int(T), c_int(heads), c_int(rank), c_int(rot), c_int(bound),
+                                                  c_int(_sm_count(qa.device)), byref(n))
+            if splits >= 1:
+                part = None
+                if n.value:
+                    part = (workspace.get("latent_attn_parts", (n.value,), torch.float32) if workspace is not None
+                            else torch.empty(n.value, dtype=torch.float32, device=qa.device))
+                self.lib.tl_latent_attn_mma.restype = c_int
+                _check(self.lib.tl_latent_attn_mma(
+                    _ptr(qa), c_int(qa.stride(0)), c_int(qa_head), _ptr(q), c_int(q.stride(0)), c_int(q_head),
+                    c_int(q_off), _ptr(pages), _ptr(out), _ptr(part), _ptr(token_pos), _ptr(token_seq),
+                    _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)), _ptr(inv_freq if dims else None),
+                    c_int(T), c_int(heads), c_int(rank), c_int(rot), c_int(dims), c_int(window or 0), c_float(scale),
+                    c_int(splits), _stream()), "latent_attn_mma")
+                if splits > 1:
+                    _check(0, "latent_attn_merge")
+                return
         _check(self._tl_latent_attn(
             _ptr(qa), c_int(qa.stride(0)), c_int(qa_head), _ptr(q), c_int(q.stride(0)), c_int(q_head), c_int(q_off),
             _ptr(pages), _ptr(out), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table),

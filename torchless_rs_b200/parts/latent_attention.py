@@ -130,12 +130,14 @@ class LatentAttention:
             qa = ws.get("latent_qa", (T, H * rank), torch.float32)
             o.headwise_gemm(q, dim + rot, self.w_uk_t, qa, rank)
             o.latent_attn(qa, rank, q, dim + rot, dim, c.pages, mix, batch.token_pos, batch.token_seq,
-                          batch.seq_slot, c.page_table, inv_freq, H, rank, rot, self.rot_dims, self.window, self.scale)
+                          batch.seq_slot, c.page_table, inv_freq, H, rank, rot, self.rot_dims, self.window, self.scale,
+                          max_keys=batch.len_bucket, workspace=ws)
         else:
             q = ws.get("latent_ql", (T, H * (rank + rot)), torch.float32)
             self.matmul(cq, self.w_q_latent, q, ops.MODE_STORE_F32)
             o.latent_attn(q, rank + rot, q, rank + rot, rank, c.pages, mix, batch.token_pos, batch.token_seq,
-                          batch.seq_slot, c.page_table, inv_freq, H, rank, rot, self.rot_dims, self.window, self.scale)
+                          batch.seq_slot, c.page_table, inv_freq, H, rank, rot, self.rot_dims, self.window, self.scale,
+                          max_keys=batch.len_bucket, workspace=ws)
         gated = ws.get("latent_gated", (T, H * vdim), rt.act_dtype)
         o.headwise_gemm(mix.view(T, H * rank), rank, self.w_uv, gated, vdim, gate=s[:, q_rank + rank + rot:])
         self.matmul(gated, self.w_o, residual, ops.MODE_STORE_F32 if overwrite else ops.MODE_ACCUM_F32)
