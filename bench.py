@@ -326,7 +326,7 @@ def design_arm(args) -> int:
                      "decode_tok_s": round(B / (ms / 1e3), 1), "weight_bytes": eng.model.weight_bytes()}
         del model, eng
         torch.cuda.empty_cache()
-    out["kernels"] = measure.kikopel_kernels(size, T, B, ctx, 24)
+    out["kernels"] = measure.kikopel_kernels(size, T, B, ctx, 24, file=sys.stderr)
     clocks.stop()
     out["clocks"] = clocks.summary(t0, clocks.mark())
     print(json.dumps(out))

@@ -272,6 +272,51 @@ def test_latent_attention_sees_exactly_its_window(dtype, rank, rot, dims, heads,
                     f"target {target} query {qpos} ({form}): {np.abs(got - ref).max():.3e}"
 
 
+@pytest.mark.parametrize("window", [None, 130])
+@pytest.mark.parametrize("heads,rank,rot", [(16, 64, 32), (5, 512, 64), (20, 128, 16)])
+def test_latent_attention_of_a_long_packed_step(window, heads, rank, rot):
+    """A step of 1300 tokens of two sequences whose border falls inside a block of the tensor-core
+    kernel (the tokens of a block share their key chunks), each continuing a sequence that already
+    holds keys; every row against numpy on the values that the pages hold."""
+    from torchless_rs_b200.cache import PAGE
+    o = _ops(torch.bfloat16)
+    rng = np.random.default_rng(rank + heads)
+    width = rank + rot
+    past, new = [70, 5], [701, 599]
+    n_pages = sum((p + n + PAGE - 1) // PAGE for p, n in zip(past, new))
+    order = rng.permutation(n_pages + 3)
+    table = np.full((4, 16), -1, dtype=np.int32)
+    slots, at = [2, 0], 0
+    for s, p, n in zip(slots, past, new):
+        k = (p + n + PAGE - 1) // PAGE
+        table[s, :k] = order[at:at + k]
+        at += k
+    store = torch.as_tensor(rng.normal(0, 0.5, (n_pages + 3, PAGE, width)), dtype=torch.bfloat16)
+    kept = store.float().numpy().astype(np.float64)
+    T = sum(new)
+    q = rng.normal(0, 0.6, (T, heads * width))
+    inv_freq = np.array([10000.0 ** (-2.0 * i / rot) for i in range(rot // 2)])
+    pos = np.concatenate([np.arange(p, p + n) for p, n in zip(past, new)])
+    seq = np.concatenate([np.full(n, i) for i, n in enumerate(new)])
+    out = torch.zeros((T, heads, rank), dtype=torch.float32).cuda()
+    qd = _dev(q)
+    o.latent_attn(qd, width, qd, width, rank, store.cuda(), out, _i32(pos), _i32(seq), _i32(slots), _i32(table),
+                  _dev(inv_freq), heads, rank, rot, rot, window, 0.25)
+    got = out.cpu().numpy()
+    q32 = q.astype(np.float32).astype(np.float64).reshape(T, heads, width)
+    worst = 0.0
+    for t in list(range(0, T, 37)) + [699, 700, 701, 702, 703, T - 1]:
+        s, p = slots[seq[t]], int(pos[t])
+        lo = max(0, p - window + 1) if window else 0
+        kk = np.stack([kept[table[s, i // PAGE], i % PAGE] for i in range(lo, p + 1)])
+        qq = np.concatenate([q32[t, :, :rank], plain.rotate(q32[t:t + 1, :, rank:], [p], 10000.0, rot)[0]], axis=-1)
+        sc = (qq @ kk.T) * 0.25
+        w = np.exp(sc - sc.max(-1, keepdims=True))
+        ref = (w / w.sum(-1, keepdims=True)) @ kk[:, :rank]
+        worst = max(worst, np.abs(got[t] - ref).max() / np.abs(ref).max())
+    assert worst <= 2e-2, f"{worst:.3e}"
+
+
 @pytest.mark.parametrize("heads,dim,vdim", [(2, 16, 8), (1, 40, 20), (3, 70, 33), (2, 128, 64)])
 def test_gated_scan_carries_its_state(heads, dim, vdim):
     """The recurrence over a batch of two sequences, whole and in pieces down to one token, from

@@ -370,37 +370,44 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// NTP: pairs of 8-column tiles of c per warp (rank <= 64 * NTP).
-template <int NTP>
-__global__ void __launch_bounds__(LM_THREADS)
+// NTP: pairs of 8-column tiles of c per warp (rank <= 64 * NTP).  TB: tokens per block, each with four
+// warps of its own; the tokens of a block that belong to one sequence share the key chunks in shared
+// memory (neighbouring positions see nearly the same keys), which divides what the block fetches
+// from the L2 cache by TB.  Keys are cut into parts (`splits` > 1) only with TB = 1.
+template <int NTP, int TB>
+__global__ void __launch_bounds__(LM_THREADS * TB)
 latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, const float* __restrict__ q, int ldq,
                        int q_head, int q_off, const __nv_bfloat16* __restrict__ pages, float* __restrict__ o,
                        float* __restrict__ part, const int* __restrict__ token_pos,
                        const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
                        const int* __restrict__ page_table, int table_stride, const float* __restrict__ inv_freq,
-                       int heads, int rank, int rot, int dims, int window, float scale, int splits) {
+                       int T, int heads, int rank, int rot, int dims, int window, float scale, int splits) {
   extern __shared__ __align__(16) unsigned char lm_smem[];
   const int width = rank + rot, pitch = width + 8;
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lm_smem);          // [16][pitch]
-  __nv_bfloat16* Ks = Qs + 16 * pitch;                                     // [LM_KC][pitch]
-  float* Ss = reinterpret_cast<float*>(Ks + LM_KC * pitch);                // [16][LM_SPITCH]
-  const __nv_bfloat16** rowp = reinterpret_cast<const __nv_bfloat16**>(Ss + 16 * LM_SPITCH);   // [LM_KC]
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lm_smem);          // [TB][16][pitch]
+  __nv_bfloat16* Ks = Qs + TB * 16 * pitch;                                // [LM_KC][pitch]
+  float* Ss_all = reinterpret_cast<float*>(Ks + LM_KC * pitch);            // [TB][16][LM_SPITCH]
+  const __nv_bfloat16** rowp = reinterpret_cast<const __nv_bfloat16**>(Ss_all + TB * 16 * LM_SPITCH);   // [LM_KC]
+  __shared__ int s_pos[TB], s_seq[TB];
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x, split = blockIdx.y, hg = blockIdx.z;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t0 = blockIdx.x * TB, split = blockIdx.y, hg = blockIdx.z;
+  const int nb = min(TB, T - t0);                  // tokens of this block
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int wg = tid >> 7, warp = (tid >> 5) & 3;  // the token's place in the block; the warp's among the token's four
   const int g = lane >> 2, qd = lane & 3;
-  const int pos = token_pos[t];
-  const int* table = page_table + (size_t)seq_slot[token_seq[t]] * table_stride;
+  if (tid < nb) { s_pos[tid] = token_pos[t0 + tid]; s_seq[tid] = token_seq[t0 + tid]; }
+  __syncthreads();
+  const int my = wg < nb ? wg : nb - 1;            // a group without a token mirrors the last one and writes nothing
+  const int pos = s_pos[my];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int n_chunks = (pos - lo + LM_KC) / LM_KC;
-  const int per_split = (n_chunks + splits - 1) / splits;
-  const int c_begin = split * per_split;
-  const int c_end = min(n_chunks, c_begin + per_split);
-  // the queries of this block's heads: [latent-space part | rotated part], times scale
+  __nv_bfloat16* Qt = Qs + wg * 16 * pitch;
+  float* Ss = Ss_all + wg * 16 * LM_SPITCH;
+  // the queries of this token's heads: [latent-space part | rotated part], times scale
   {
     const int half = dims >> 1;
-    for (int idx = tid; idx < 16 * width; idx += LM_THREADS) {
+    const int t = t0 + my;
+    for (int idx = tid & (LM_THREADS - 1); idx < 16 * width; idx += LM_THREADS) {
       const int r = idx / width, d = idx - r * width, h = hg * 16 + r;
       float v = 0.0f;
       if (h < heads) {
@@ -421,7 +428,7 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
         }
         v *= scale;
       }
-      Qs[r * pitch + d] = __float2bfloat16_rn(v);
+      Qt[r * pitch + d] = __float2bfloat16_rn(v);
     }
   }
   float acc[2 * NTP][4];
@@ -430,107 +437,127 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};   // rows g and g + 8
   const int n_pairs = rank >> 4;        // groups of 16 columns of c
   const int vecs = width >> 3;          // 16-byte pieces per row
-  for (int c = c_begin; c < c_end; ++c) {
-    const int base = lo + c * LM_KC;
-    __syncthreads();     // the chunk before is done with Ks, Ss and rowp (and Qs is written)
-    if (tid < LM_KC) {
-      const int i = base + tid;
-      rowp[tid] = i <= pos ? pages + ((size_t)table[i / TL_PAGE] * TL_PAGE + (i % TL_PAGE)) * width : nullptr;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < LM_KC * vecs; idx += LM_THREADS) {
-      const int r = idx / vecs, v = idx - r * vecs;
-      __nv_bfloat16* dst = Ks + r * pitch + v * 8;
-      if (rowp[r] != nullptr) {
-        const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(rowp[r] + v * 8) : "memory");
-      } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+  // runs of tokens of one sequence (a block may straddle the end of a sequence of the packed batch)
+  for (int r_begin = 0; r_begin < nb;) {
+    int r_end = r_begin + 1;
+    while (r_end < nb && s_seq[r_end] == s_seq[r_begin]) ++r_end;
+    const bool active = wg >= r_begin && wg < r_end;
+    const int* table = page_table + (size_t)seq_slot[s_seq[r_begin]] * table_stride;
+    const int p_first = s_pos[r_begin], p_last = s_pos[r_end - 1];
+    const int lo_min = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+    const int n_chunks = (p_last - lo_min + LM_KC) / LM_KC;
+    const int per_split = (n_chunks + splits - 1) / splits;
+    const int c_begin = split * per_split;
+    const int c_end = min(n_chunks, c_begin + per_split);
+    for (int c = c_begin; c < c_end; ++c) {
+      const int base = lo_min + c * LM_KC;
+      __syncthreads();     // the chunk before is done with Ks, Ss and rowp (and Qs is written)
+      if (tid < LM_KC) {
+        const int i = base + tid;
+        rowp[tid] = i <= p_last ? pages + ((size_t)table[i / TL_PAGE] * TL_PAGE + (i % TL_PAGE)) * width : nullptr;
       }
-    }
-    asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-    // scores of this warp's 16 keys
-    float sc[2][4] = {};
-    {
-      const __nv_bfloat16* qrow = Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (lane >> 4) * 8;
-      const __nv_bfloat16* krow = Ks + (warp * 16 + (lane >> 4) * 8 + (lane & 7)) * pitch + ((lane >> 3) & 1) * 8;
-      for (int ks = 0; ks < width; ks += 16) {
-        uint32_t a[4], b[4];
-        ldsm_x4(a, qrow + ks);
-        ldsm_x4(b, krow + ks);
-        mma_bf16(sc[0], a, b[0], b[1]);
-        mma_bf16(sc[1], a, b[2], b[3]);
+      __syncthreads();
+      for (int idx = tid; idx < LM_KC * vecs; idx += LM_THREADS * TB) {
+        const int r = idx / vecs, v = idx - r * vecs;
+        __nv_bfloat16* dst = Ks + r * pitch + v * 8;
+        if (rowp[r] != nullptr) {
+          const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(rowp[r] + v * 8) : "memory");
+        } else {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
-    }
+      asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();
+      // scores of this warp's 16 keys
+      if (active) {
+        float sc[2][4] = {};
+        const __nv_bfloat16* qrow = Qt + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (lane >> 4) * 8;
+        const __nv_bfloat16* krow = Ks + (warp * 16 + (lane >> 4) * 8 + (lane & 7)) * pitch + ((lane >> 3) & 1) * 8;
+        for (int ks = 0; ks < width; ks += 16) {
+          uint32_t a[4], b[4];
+          ldsm_x4(a, qrow + ks);
+          ldsm_x4(b, krow + ks);
+          mma_bf16(sc[0], a, b[0], b[1]);
+          mma_bf16(sc[1], a, b[2], b[3]);
+        }
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const int col = warp * 16 + nt * 8 + qd * 2;
-      const bool v0 = base + col <= pos, v1 = base + col + 1 <= pos;
-      Ss[g * LM_SPITCH + col] = v0 ? sc[nt][0] : -INFINITY;
-      Ss[g * LM_SPITCH + col + 1] = v1 ? sc[nt][1] : -INFINITY;
-      Ss[(g + 8) * LM_SPITCH + col] = v0 ? sc[nt][2] : -INFINITY;
-      Ss[(g + 8) * LM_SPITCH + col + 1] = v1 ? sc[nt][3] : -INFINITY;
-    }
-    __syncthreads();
-    // softmax over the chunk, per row; the weights as A operands of the second product
-    float s[2][LM_KC / 16][4];
-    float cmax[2] = {-INFINITY, -INFINITY};
+        for (int nt = 0; nt < 2; ++nt) {
+          const int col = warp * 16 + nt * 8 + qd * 2;
+          const int k0 = base + col;
+          const bool v0 = k0 >= lo && k0 <= pos, v1 = k0 + 1 >= lo && k0 + 1 <= pos;
+          Ss[g * LM_SPITCH + col] = v0 ? sc[nt][0] : -INFINITY;
+          Ss[g * LM_SPITCH + col + 1] = v1 ? sc[nt][1] : -INFINITY;
+          Ss[(g + 8) * LM_SPITCH + col] = v0 ? sc[nt][2] : -INFINITY;
+          Ss[(g + 8) * LM_SPITCH + col + 1] = v1 ? sc[nt][3] : -INFINITY;
+        }
+      }
+      __syncthreads();
+      if (!active) continue;
+      // softmax over the chunk, per row; the weights as A operands of the second product
+      float s[2][LM_KC / 16][4];
+      float cmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int kk = 0; kk < LM_KC / 16; ++kk) {
+          const float2 x = *reinterpret_cast<const float2*>(Ss + (g + 8 * r) * LM_SPITCH + kk * 16 + qd * 2);
+          const float2 y = *reinterpret_cast<const float2*>(Ss + (g + 8 * r) * LM_SPITCH + kk * 16 + 8 + qd * 2);
+          s[r][kk][0] = x.x; s[r][kk][1] = x.y; s[r][kk][2] = y.x; s[r][kk][3] = y.y;
+          cmax[r] = fmaxf(cmax[r], fmaxf(fmaxf(x.x, x.y), fmaxf(y.x, y.y)));
+        }
+      float alpha[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        cmax[r] = fmaxf(cmax[r], __shfl_xor_sync(0xffffffffu, cmax[r], 1));
+        cmax[r] = fmaxf(cmax[r], __shfl_xor_sync(0xffffffffu, cmax[r], 2));
+        // The first chunk of a token's range holds a key it sees, so the maximum is finite from then on; a
+        // later chunk in which this token sees no key (only a neighbour does) leaves everything as it is.
+        const float m_new = fmaxf(m_run[r], cmax[r]);
+        alpha[r] = m_new == -INFINITY ? 1.0f : expf(m_run[r] - m_new);      // 0 at the first chunk
+        float sum = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < LM_KC / 16; ++kk)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s[r][kk][e] = m_new == -INFINITY ? 0.0f : expf(s[r][kk][e] - m_new);   // 0 for keys not seen
+            sum += s[r][kk][e];
+          }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_run[r] = l_run[r] * alpha[r] + sum;
+        m_run[r] = m_new;
+      }
+#pragma unroll
+      for (int i = 0; i < 2 * NTP; ++i) {
+        acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];
+        acc[i][2] *= alpha[1]; acc[i][3] *= alpha[1];
+      }
 #pragma unroll
       for (int kk = 0; kk < LM_KC / 16; ++kk) {
-        const float2 x = *reinterpret_cast<const float2*>(Ss + (g + 8 * r) * LM_SPITCH + kk * 16 + qd * 2);
-        const float2 y = *reinterpret_cast<const float2*>(Ss + (g + 8 * r) * LM_SPITCH + kk * 16 + 8 + qd * 2);
-        s[r][kk][0] = x.x; s[r][kk][1] = x.y; s[r][kk][2] = y.x; s[r][kk][3] = y.y;
-        cmax[r] = fmaxf(cmax[r], fmaxf(fmaxf(x.x, x.y), fmaxf(y.x, y.y)));
-      }
-    float alpha[2];
+        uint32_t a[4];
+        a[0] = pack_bf16(s[0][kk][0], s[0][kk][1]);
+        a[1] = pack_bf16(s[1][kk][0], s[1][kk][1]);
+        a[2] = pack_bf16(s[0][kk][2], s[0][kk][3]);
+        a[3] = pack_bf16(s[1][kk][2], s[1][kk][3]);
+        const __nv_bfloat16* vrow = Ks + (kk * 16 + (lane & 15)) * pitch + (lane >> 4) * 8;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      cmax[r] = fmaxf(cmax[r], __shfl_xor_sync(0xffffffffu, cmax[r], 1));
-      cmax[r] = fmaxf(cmax[r], __shfl_xor_sync(0xffffffffu, cmax[r], 2));
-      const float m_new = fmaxf(m_run[r], cmax[r]);      // finite: a chunk holds at least one visible key
-      alpha[r] = expf(m_run[r] - m_new);                 // 0 at the first chunk
-      float sum = 0.0f;
-#pragma unroll
-      for (int kk = 0; kk < LM_KC / 16; ++kk)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          s[r][kk][e] = expf(s[r][kk][e] - m_new);       // exp(-inf) = 0 for keys beyond the position
-          sum += s[r][kk][e];
-        }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      l_run[r] = l_run[r] * alpha[r] + sum;
-      m_run[r] = m_new;
-    }
-#pragma unroll
-    for (int i = 0; i < 2 * NTP; ++i) {
-      acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];
-      acc[i][2] *= alpha[1]; acc[i][3] *= alpha[1];
-    }
-#pragma unroll
-    for (int kk = 0; kk < LM_KC / 16; ++kk) {
-      uint32_t a[4];
-      a[0] = pack_bf16(s[0][kk][0], s[0][kk][1]);
-      a[1] = pack_bf16(s[1][kk][0], s[1][kk][1]);
-      a[2] = pack_bf16(s[0][kk][2], s[0][kk][3]);
-      a[3] = pack_bf16(s[1][kk][2], s[1][kk][3]);
-      const __nv_bfloat16* vrow = Ks + (kk * 16 + (lane & 15)) * pitch + (lane >> 4) * 8;
-#pragma unroll
-      for (int i = 0; i < NTP; ++i) {
-        const int pair = warp + 4 * i;
-        if (pair < n_pairs) {
-          uint32_t b[4];
-          ldsm_x4_trans(b, vrow + pair * 16);
-          mma_bf16(acc[2 * i], a, b[0], b[1]);
-          mma_bf16(acc[2 * i + 1], a, b[2], b[3]);
+        for (int i = 0; i < NTP; ++i) {
+          const int pair = warp + 4 * i;
+          if (pair < n_pairs) {
+            uint32_t b[4];
+            ldsm_x4_trans(b, vrow + pair * 16);
+            mma_bf16(acc[2 * i], a, b[0], b[1]);
+            mma_bf16(acc[2 * i + 1], a, b[2], b[3]);
+          }
         }
       }
     }
+    r_begin = r_end;
   }
+  if (wg >= nb) return;
   // out: normalised if this block saw all the keys, else this part's sums with its maximum and sum
+  const int t = t0 + wg;
   const int hpad = gridDim.z * 16;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -597,7 +624,7 @@ extern "C" int tl_latent_attn_plan(int T, int heads, int rank, int rot, int max_
   *part_floats = 0;
   if (rank % 16 || rot % 16 || rank > 512 || rank <= 0) return 0;     // the CUDA-core kernel
   const size_t smem = (size_t)(16 + LM_KC) * (rank + rot + 8) * 2 + 16 * LM_SPITCH * 4 + LM_KC * 8;
-  if (smem > 200 * 1024) return 0;
+  if (smem > 200 * 1024) return 0;      // (one token a block; lm_smem_bytes(1, ...) below)
   const int groups = (heads + 15) / 16;
   const long long blocks = (long long)T * groups;
   int splits = 1;
@@ -612,6 +639,10 @@ extern "C" int tl_latent_attn_plan(int T, int heads, int rank, int rot, int max_
   return splits;
 }
 
+static size_t lm_smem_bytes(int tb, int rank, int rot) {
+  return (size_t)(16 * tb + LM_KC) * (rank + rot + 8) * 2 + (size_t)tb * 16 * LM_SPITCH * 4 + LM_KC * 8;
+}
+
 extern "C" int tl_latent_attn_mma(const float* qa, int ld_qa, int qa_head, const float* q, int ldq, int q_head,
                                   int q_off, const void* pages, float* o, float* part, const int* token_pos,
                                   const int* token_seq, const int* seq_slot, const int* page_table,
@@ -623,27 +654,34 @@ extern "C" int tl_latent_attn_mma(const float* qa, int ld_qa, int qa_head, const
     return TL_ERR_UNSUPPORTED;
   const int groups = (heads + 15) / 16;
   if (splits > 65535 || groups > 65535) return TL_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)(16 + LM_KC) * (rank + rot + 8) * 2 + 16 * LM_SPITCH * 4 + LM_KC * 8;
-  dim3 grid(T, splits, groups);
+  // four tokens a block where there are tokens enough to fill the GPU that way and the block fits
+  const bool many = splits == 1 && (long long)T * groups >= 8LL * 148 && lm_smem_bytes(4, rank, rot) <= 200 * 1024;
+  const int tb = many ? 4 : 1;
+  const size_t smem = lm_smem_bytes(tb, rank, rot);
+  dim3 grid((T + tb - 1) / tb, splits, groups);
   int rc;
-#define LM_LAUNCH(NTP)                                                                                      \
-  {                                                                                                         \
-    static bool set = false;                                                                                \
-    if (!set) {                                                                                             \
-      if (cudaFuncSetAttribute(latent_attn_mma_kernel<NTP>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
-                               200 * 1024) != cudaSuccess)                                                  \
-        return TL_ERR_UNSUPPORTED;                                                                          \
-      set = true;                                                                                           \
-    }                                                                                                       \
-    rc = tl_launch(latent_attn_mma_kernel<NTP>, grid, dim3(LM_THREADS), smem, stream, qa, ld_qa, qa_head, q, \
-                   ldq, q_head, q_off, (const __nv_bfloat16*)pages, o, part, token_pos, token_seq, seq_slot, \
-                   page_table, table_stride, inv_freq, heads, rank, rot, dims, window, scale, splits);       \
+#define LM_LAUNCH_TB(NTP, TBV)                                                                               \
+  {                                                                                                          \
+    static bool set = false;                                                                                 \
+    if (!set) {                                                                                              \
+      if (cudaFuncSetAttribute(latent_attn_mma_kernel<NTP, TBV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                               200 * 1024) != cudaSuccess)                                                   \
+        return TL_ERR_UNSUPPORTED;                                                                           \
+      set = true;                                                                                            \
+    }                                                                                                        \
+    rc = tl_launch(latent_attn_mma_kernel<NTP, TBV>, grid, dim3(LM_THREADS * TBV), smem, stream, qa, ld_qa,  \
+                   qa_head, q, ldq, q_head, q_off, (const __nv_bfloat16*)pages, o, part, token_pos, token_seq, \
+                   seq_slot, page_table, table_stride, inv_freq, T, heads, rank, rot, dims, window, scale,   \
+                   splits);                                                                                  \
   }
+#define LM_LAUNCH(NTP) \
+  { if (many) LM_LAUNCH_TB(NTP, 4) else LM_LAUNCH_TB(NTP, 1) }
   if (rank <= 64) LM_LAUNCH(1)
   else if (rank <= 128) LM_LAUNCH(2)
   else if (rank <= 256) LM_LAUNCH(4)
   else LM_LAUNCH(8)
 #undef LM_LAUNCH
+#undef LM_LAUNCH_TB
   if (rc != 0 || splits == 1) return rc;
   return tl_launch(latent_attn_merge_kernel, dim3(T, heads), dim3(128), 0, stream, (const float*)part, o, heads,
                    groups * 16, rank, splits);

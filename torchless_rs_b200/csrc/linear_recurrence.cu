@@ -13,11 +13,48 @@
 // them rather than stored and read again.
 #include "common.cuh"
 
-#define SCAN_COLS 4          // columns per warp
+#define SCAN_COLS 4          // columns per warp (warp_sum4 is written for 4)
 #define SCAN_WARPS 4         // warps per block
 #define SCAN_MAX_R 8         // rows per lane: dim <= 256
 
-template <int R>
+// The gates of all tokens at once, in place: zq <- silu(zq), zf <- low + (1 - low) sigmoid(zf + bias).
+// For steps of many tokens per sequence, so that the sequential walk below is left with the
+// recurrence alone.
+__global__ void scan_gates_kernel(float* __restrict__ zq, float* __restrict__ zf, int ld,
+                                  const float* __restrict__ bias, const float* __restrict__ low, int T, int hd) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t total = (size_t)T * hd;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / hd;
+    const int i = (int)(idx - t * hd);
+    const float z = zq[t * ld + i];
+    zq[t * ld + i] = z / (1.0f + expf(-z));
+    const float l = low[i];
+    zf[t * ld + i] = l + (1.0f - l) * (1.0f / (1.0f + expf(-(zf[t * ld + i] + bias[i]))));
+  }
+}
+
+// Sums over the warp of SCAN_COLS (4) values per lane with 6 shuffles instead of 20: two steps hand
+// half of the columns to the other half of the lanes, three more finish the one column a lane is
+// left with.  Lane 8 k (k = 0..3) ends with the sum of column (k / 2) * 2 + k % 2 = k.
+__device__ __forceinline__ float warp_sum4(const float (&part)[SCAN_COLS], int lane) {
+  const bool hi = lane & 16;
+  float k0 = hi ? part[2] : part[0], k1 = hi ? part[3] : part[1];
+  k0 += __shfl_xor_sync(0xffffffffu, hi ? part[0] : part[2], 16);
+  k1 += __shfl_xor_sync(0xffffffffu, hi ? part[1] : part[3], 16);
+  const bool b = lane & 8;
+  float k = b ? k1 : k0;
+  k += __shfl_xor_sync(0xffffffffu, b ? k0 : k1, 8);
+  k += __shfl_xor_sync(0xffffffffu, k, 4);
+  k += __shfl_xor_sync(0xffffffffu, k, 2);
+  k += __shfl_xor_sync(0xffffffffu, k, 1);
+  return k;
+}
+
+// PRE: zq and zf already hold q and f (scan_gates_kernel ran).
+template <int R, bool PRE>
 __global__ void __launch_bounds__(SCAN_WARPS * 32)
 gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, const float* __restrict__ zv,
                   int ld, const float* __restrict__ bias, const float* __restrict__ low,
@@ -62,14 +99,18 @@ gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, co
 #pragma unroll
       for (int c = 0; c < SCAN_COLS; ++c) vv[p][c] = c0 + c < vdim ? rv[c] : 0.0f;
     }
+    if (!PRE) {
 #pragma unroll
-    for (int p = 0; p < PF; ++p)
+      for (int p = 0; p < PF; ++p)
+        if (tb + p < t1) {
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const float z = qv[p][r];
-        qv[p][r] = z / (1.0f + expf(-z));
-        fv[p][r] = lo[r] + (1.0f - lo[r]) * (1.0f / (1.0f + expf(-(fv[p][r] + bi[r]))));
-      }
+          for (int r = 0; r < R; ++r) {
+            const float z = qv[p][r];
+            qv[p][r] = z / (1.0f + expf(-z));
+            fv[p][r] = lo[r] + (1.0f - lo[r]) * (1.0f / (1.0f + expf(-(fv[p][r] + bi[r]))));
+          }
+        }
+    }
 #pragma unroll
     for (int p = 0; p < PF; ++p) {
       if (tb + p < t1) {
@@ -87,13 +128,9 @@ gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, co
             }
           }
         }
-#pragma unroll
-        for (int c = 0; c < SCAN_COLS; ++c) part[c] = warp_sum(part[c]);
-        if (lane == 0) {
-#pragma unroll
-          for (int c = 0; c < SCAN_COLS; ++c)
-            if (c0 + c < vdim) o[(size_t)(tb + p) * ldo + h * vdim + c0 + c] = part[c];
-        }
+        const float sum = warp_sum4(part, lane);
+        const int c = lane >> 3;
+        if ((lane & 7) == 0 && c0 + c < vdim) o[(size_t)(tb + p) * ldo + h * vdim + c0 + c] = sum;
       }
     }
   }
@@ -109,20 +146,33 @@ gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, co
 // zq, zf, zv: [T, ld] 32-bit (columns of one stacked product); bias, low: [heads * dim] 32-bit;
 // state: [slots, heads, dim, vdim] 32-bit; o: [T, ldo] 32-bit; B sequences, sequence b owning the
 // tokens seq_start[b] .. seq_start[b + 1] - 1 of the step.
-extern "C" int TL_NAME(tl_gated_scan)(const float* zq, const float* zf, const float* zv, int ld, const float* bias,
+// `zq` and `zf` are overwritten with q and f when the step has many tokens per sequence (T > 4 B).
+extern "C" int TL_NAME(tl_gated_scan)(float* zq, float* zf, const float* zv, int ld, const float* bias,
                                       const float* low, float* state, float* o, int ldo, const int* seq_start,
-                                      const int* seq_slot, int B, int heads, int dim, int vdim,
+                                      const int* seq_slot, int T, int B, int heads, int dim, int vdim,
                                       cudaStream_t stream) {
-  if (B <= 0) return 0;
+  if (B <= 0 || T <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0) return TL_ERR_BAD_ARG;
   if (dim > 32 * SCAN_MAX_R || heads > 65535) return TL_ERR_UNSUPPORTED;
   const int per_block = SCAN_WARPS * SCAN_COLS;
   dim3 grid(B, heads, (vdim + per_block - 1) / per_block);
   if (grid.z > 65535) return TL_ERR_UNSUPPORTED;
   const int R = (dim + 31) / 32;
-#define SCAN(RR)                                                                                        \
-  return tl_launch(gated_scan_kernel<RR>, grid, dim3(SCAN_WARPS * 32), 0, stream, zq, zf, zv, ld, bias, \
-                   low, state, o, ldo, seq_start, seq_slot, heads, dim, vdim)
+  const bool pre = T > 4 * B;
+  if (pre) {
+    const size_t total = (size_t)T * heads * dim;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    const int rc = tl_launch(scan_gates_kernel, dim3(blocks), dim3(256), 0, stream, zq, zf, ld, bias, low, T,
+                             heads * dim);
+    if (rc != 0) return rc;
+  }
+#define SCAN(RR)                                                                                               \
+  return pre ? tl_launch(gated_scan_kernel<RR, true>, grid, dim3(SCAN_WARPS * 32), 0, stream,                  \
+                         (const float*)zq, (const float*)zf, zv, ld, bias, low, state, o, ldo, seq_start,      \
+                         seq_slot, heads, dim, vdim)                                                           \
+             : tl_launch(gated_scan_kernel<RR, false>, grid, dim3(SCAN_WARPS * 32), 0, stream,                 \
+                         (const float*)zq, (const float*)zf, zv, ld, bias, low, state, o, ldo, seq_start,      \
+                         seq_slot, heads, dim, vdim)
   switch (R) {
     case 1: SCAN(1);
     case 2: SCAN(2);

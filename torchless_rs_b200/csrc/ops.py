@@ -457,7 +457,8 @@ class CoreOps:
                    vdim: int) -> None:
         """The recurrence S <- diag(f) S + (1 - f) v^T, o = S^T q over each sequence's tokens of the step,
         from and into `state` [slots, heads, dim, vdim]; `z` [T, 2 heads dim + heads vdim] 32-bit holds the
-        projections for q, f and v side by side."""
+        projections for q, f and v side by side (for steps of many tokens per sequence the q and f columns
+        are overwritten with their activations)."""
         _need(z, torch.float32, "recurrence projections", contiguous=False)
         for t, n in ((bias, "forget bias"), (low, "forget lower bound"), (state, "recurrent state"),
                      (out, "recurrence out")):
@@ -469,8 +470,10 @@ class CoreOps:
             raise KernelError("gated_scan: sizes do not match")
         _check(self._tl_gated_scan(_ptr(z), _ptr(z[:, hd:]), _ptr(z[:, 2 * hd:]), c_int(z.stride(0)), _ptr(bias),
                                    _ptr(low), _ptr(state), _ptr(out), c_int(out.stride(0)), _ptr(seq_start),
-                                   _ptr(seq_slot), c_int(seq_slot.numel()), c_int(heads), c_int(dim), c_int(vdim),
-                                   _stream()), "gated_scan")
+                                   _ptr(seq_slot), c_int(T), c_int(seq_slot.numel()), c_int(heads), c_int(dim),
+                                   c_int(vdim), _stream()), "gated_scan")
+        if T > 4 * seq_slot.numel():
+            _check(0, "scan_gates")
 
 
 class SamplingOps:

@@ -204,7 +204,7 @@ def mistral_like(size: str, layers: int) -> dict:
                 vocab_size=z["vocab"], sliding_window=z["window"], max_position_embeddings=32768)
 
 
-def kikopel_kernels(size: str, T: int, B: int, ctx: int, iters: int) -> list:
+def kikopel_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) -> list:
     """Every kernel of the Kikopel design alone at the sizes `size`, for a prompt of T tokens and for a decode
     step of B sequences at a context of `ctx`, beside the like kernel of the Mistral path at equal sizes.
     Returns rows (name, case, microseconds, fraction of the roofline, what bounds it) and prints them.  The
@@ -231,7 +231,7 @@ def kikopel_kernels(size: str, T: int, B: int, ctx: int, iters: int) -> list:
         frac = max(t_mem, t_fl) / us
         rows.append({"kernel": name, "case": case, "us": round(us, 2), "roofline_frac": round(frac, 4),
                      "bound": "memory" if t_mem >= t_fl else "tensor"})
-        print(f"{name:28s} {case:22s} {us:10.2f} us   {frac:7.4f} of the roofline ({rows[-1]['bound']})")
+        print(f"{name:28s} {case:22s} {us:10.2f} us   {frac:7.4f} of the roofline ({rows[-1]['bound']})", file=file)
 
     inv = torch.tensor([1e6 ** (-2.0 * i / rot) for i in range(rot // 2)], device=dev)
     for case, n_tok, seqs, past in ((f"prompt {T}", T, 1, 0), (f"decode {B} x {ctx}", B, B, ctx - 1)):
