@@ -430,11 +430,12 @@ def test_branch_norm_add_and_poly_norm(dtype, rows, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("M,heads,N,K", [(1, 3, 20, 24), (16, 2, 7, 40), (17, 1, 70, 33), (200, 4, 48, 96)])
+@pytest.mark.parametrize("M,heads,N,K", [(1, 3, 20, 24), (16, 2, 7, 40), (17, 1, 70, 33), (200, 4, 48, 96),
+                                         (130, 3, 80, 64), (64, 2, 128, 512), (300, 17, 10, 24)])
 def test_headwise_products(dtype, M, heads, N, K):
     o = _ops(dtype)
     rng = np.random.default_rng(M)
-    a_head, c_head = K + 5, N + 3
+    a_head, c_head = K + (8 if K % 8 == 0 else 5), N + 3     # aligned strides let the tensor-core kernel run
     a = rng.normal(0, 1, (M, heads * a_head))
     w = torch.as_tensor(rng.normal(0, 1, (heads, N, K)), dtype=dtype).cuda()
     w64 = w.double().cpu().numpy()

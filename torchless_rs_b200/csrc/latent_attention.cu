@@ -686,4 +686,99 @@ extern "C" int tl_latent_attn_mma(const float* qa, int ld_qa, int qa_head, const
   return tl_launch(latent_attn_merge_kernel, dim3(T, heads), dim3(128), 0, stream, (const float*)part, o, heads,
                    groups * 16, rank, splits);
 }
+
+// ---------------------------------------------------------------------------
+// The per-head value up-projection with the output gate on tensor cores (bfloat16 build), for steps of
+// many tokens:  C[t, h, n] = sigmoid(G[t, h N + n]) * sum_k A[t, h, k] W[h, n, k],  A 32-bit (rounded to
+// bfloat16 on its way into shared memory), W and C bfloat16.  A block computes 64 rows x 64 outputs of
+// one head; each of its four warps 16 rows; K goes in steps of 32 through shared memory.
+// ---------------------------------------------------------------------------
+#define HM_BM 64
+#define HM_BN 64
+#define HM_BK 32
+#define HM_PITCH (HM_BK + 8)
+
+__global__ void __launch_bounds__(128)
+headwise_mma_kernel(const float* __restrict__ A, int lda, int a_head, const __nv_bfloat16* __restrict__ W,
+                    __nv_bfloat16* __restrict__ C, int ldc, int c_head, const float* __restrict__ G, int ldg,
+                    int M, int N, int K) {
+  __shared__ __align__(16) __nv_bfloat16 As[HM_BM * HM_PITCH];
+  __shared__ __align__(16) __nv_bfloat16 Ws[HM_BN * HM_PITCH];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int h = blockIdx.z, m0 = blockIdx.y * HM_BM, n0 = blockIdx.x * HM_BN;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, qd = lane & 3;
+  const float* Ah = A + (size_t)h * a_head;
+  const __nv_bfloat16* Wh = W + (size_t)h * N * K;
+  float acc[HM_BN / 8][4];
+#pragma unroll
+  for (int i = 0; i < HM_BN / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+  for (int k0 = 0; k0 < K; k0 += HM_BK) {
+    __syncthreads();     // the step before has read both tiles
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {                      // A: 64 rows x 8 pieces of four 32-bit numbers
+      const int idx = tid + i * 128, r = idx >> 3, c4 = (idx & 7) * 4;
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (m0 + r < M && k0 + c4 < K) v = *reinterpret_cast<const float4*>(Ah + (size_t)(m0 + r) * lda + k0 + c4);
+      uint2 u;
+      u.x = pack_bf16(v.x, v.y);
+      u.y = pack_bf16(v.z, v.w);
+      *reinterpret_cast<uint2*>(As + r * HM_PITCH + c4) = u;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {                      // W: 64 rows x 4 pieces of eight bfloat16
+      const int idx = tid + i * 128, r = idx >> 2, c8 = (idx & 3) * 8;
+      __nv_bfloat16* dst = Ws + r * HM_PITCH + c8;
+      if (n0 + r < N && k0 + c8 < K) {
+        const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(Wh + (size_t)(n0 + r) * K + k0 + c8)
+                     : "memory");
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < HM_BK; ks += 16) {
+      uint32_t a[4];
+      ldsm_x4(a, As + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * HM_PITCH + ks + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < HM_BN / 16; ++np) {
+        uint32_t b[4];
+        ldsm_x4(b, Ws + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * HM_PITCH + ks + ((lane >> 3) & 1) * 8);
+        mma_bf16(acc[2 * np], a, b[0], b[1]);
+        mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int m = m0 + warp * 16 + g + 8 * r;
+    if (m >= M) continue;
+#pragma unroll
+    for (int nt = 0; nt < HM_BN / 8; ++nt) {
+      const int n = n0 + nt * 8 + qd * 2;
+      if (n >= N) continue;          // N is even (checked by the launcher), so n + 1 < N too
+      const float2 gt = *reinterpret_cast<const float2*>(G + (size_t)m * ldg + (size_t)h * N + n);
+      const float v0 = acc[nt][2 * r] * (1.0f / (1.0f + expf(-gt.x)));
+      const float v1 = acc[nt][2 * r + 1] * (1.0f / (1.0f + expf(-gt.y)));
+      *reinterpret_cast<uint32_t*>(C + (size_t)m * ldc + (size_t)h * c_head + n) = pack_bf16(v0, v1);
+    }
+  }
+}
+
+// Returns TL_ERR_UNSUPPORTED for sizes or alignments it does not take (the FFMA kernel then runs).
+extern "C" int tl_headwise_mma(const float* A, int lda, int a_head, const void* W, void* C, int ldc, int c_head,
+                               const float* G, int ldg, int M, int N, int K, int heads, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || heads <= 0) return 0;
+  if (K % 8 || N % 2 || lda % 4 || a_head % 4 || ldc % 2 || c_head % 2 || ldg % 2 || G == nullptr ||
+      ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)C & 3) || ((uintptr_t)G & 7) || heads > 65535 ||
+      (M + HM_BM - 1) / HM_BM > 65535)
+    return TL_ERR_UNSUPPORTED;
+  dim3 grid((N + HM_BN - 1) / HM_BN, (M + HM_BM - 1) / HM_BM, heads);
+  return tl_launch(headwise_mma_kernel, grid, dim3(128), 0, stream, A, lda, a_head, (const __nv_bfloat16*)W,
+                   (__nv_bfloat16*)C, ldc, c_head, G, ldg, M, N, K);
+}
 #endif

@@ -397,6 +397,15 @@ class CoreOps:
             if gate.shape != (M, heads * N) or gate.stride(1) != 1:
                 raise KernelError("headwise_gemm: the gate must be [rows, heads * outputs]")
             ldg = gate.stride(0)
+        if gate is not None and M > 16 and self.act_dtype == torch.bfloat16:
+            # many rows: the tensor-core kernel, where sizes and alignments allow it
+            self.lib.tl_headwise_mma.restype = c_int
+            st = self.lib.tl_headwise_mma(_ptr(a), c_int(a.stride(0)), c_int(a_head), _ptr(w), _ptr(c),
+                                          c_int(c.stride(0)), c_int(c_head), _ptr(gate), c_int(ldg), c_int(M),
+                                          c_int(N), c_int(K), c_int(heads), _stream())
+            if st != -2:
+                _check(st, "headwise_mma")
+                return
         _check(self._tl_headwise_gemm(_ptr(a), c_int(a.stride(0)), c_int(a_head), _ptr(w), _ptr(c),
                                       c_int(c.stride(0)), c_int(c_head), _ptr(gate), c_int(ldg), c_int(M), c_int(N),
                                       c_int(K), c_int(heads), c_int(0 if gate is None else 1), _stream()),
