@@ -324,7 +324,7 @@ def test_gated_scan_carries_its_state(heads, dim, vdim):
     starts a new sequence.  Decays close to one, so that the first tokens still count at the end."""
     o = _ops(torch.float32)
     rng = np.random.default_rng(dim)
-    lens = [150, 47]
+    lens = [300, 47]      # 300: long enough for the path that shares the state's rows out over several warps
     T, hd = sum(lens), heads * dim
     z = rng.normal(0, 1.0, (T, 2 * hd + heads * vdim))
     bias, low = rng.normal(2.0, 1.0, hd), rng.uniform(0.5, 0.99, hd)
@@ -341,7 +341,7 @@ def test_gated_scan_carries_its_state(heads, dim, vdim):
         refs.append((out.reshape(n, heads * vdim), S))
         at += n
     slots = [4, 1]
-    for cuts in ([150], [1] * 10 + [2, 3, 64, 71], [149, 1]):
+    for cuts in ([300], [1] * 10 + [2, 3, 64, 71, 150], [299, 1]):
         state = torch.full((6, heads, dim, vdim), 7.0).cuda()
         state[slots] = 0.0
         got = [np.zeros((n, heads * vdim)) for n in lens]

@@ -59,12 +59,17 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32)
 gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, const float* __restrict__ zv,
                   int ld, const float* __restrict__ bias, const float* __restrict__ low,
                   float* __restrict__ state, float* __restrict__ o, int ldo, const int* __restrict__ seq_start,
-                  const int* __restrict__ seq_slot, int heads, int dim, int vdim) {
+                  const int* __restrict__ seq_slot, int heads, int dim, int vdim, int row_groups, int T) {
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c0 = (blockIdx.z * SCAN_WARPS + warp) * SCAN_COLS;
+  // With row_groups > 1 a warp holds the rows row0 .. row0 + 32 R - 1 only and its sums over them go to
+  // slice `rg` of `o` ([row_groups][T][ldo]); scan_sum_slices_kernel adds the slices.
+  const int rg = blockIdx.z % row_groups;
+  const int row0 = rg * 32 * R;
+  o += (size_t)rg * T * ldo;
+  const int c0 = ((blockIdx.z / row_groups) * SCAN_WARPS + warp) * SCAN_COLS;
   if (c0 >= vdim) return;
   const int t0 = seq_start[b], t1 = seq_start[b + 1];
   float* S = state + (((size_t)seq_slot[b] * heads + h) * dim) * vdim;
@@ -72,7 +77,7 @@ gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, co
   float lo[R], bi[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = lane + 32 * r;
+    const int i = row0 + lane + 32 * r;
     lo[r] = i < dim ? low[h * dim + i] : 0.0f;
     bi[r] = i < dim ? bias[h * dim + i] : 0.0f;
 #pragma unroll
@@ -92,7 +97,7 @@ gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, co
       const float* rv = zv + (size_t)t * ld + h * vdim + c0;
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        const int i = lane + 32 * r;
+        const int i = row0 + lane + 32 * r;
         qv[p][r] = i < dim ? rq[i] : 0.0f;
         fv[p][r] = i < dim ? rf[i] : 0.0f;
       }
@@ -119,7 +124,7 @@ gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, co
         for (int c = 0; c < SCAN_COLS; ++c) part[c] = 0.0f;
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-          if (lane + 32 * r < dim) {
+          if (row0 + lane + 32 * r < dim) {
             const float f = fv[p][r], w = 1.0f - f;
 #pragma unroll
             for (int c = 0; c < SCAN_COLS; ++c) {
@@ -136,10 +141,21 @@ gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, co
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = lane + 32 * r;
+    const int i = row0 + lane + 32 * r;
 #pragma unroll
     for (int c = 0; c < SCAN_COLS; ++c)
       if (i < dim && c0 + c < vdim) S[(size_t)i * vdim + c0 + c] = s[r][c];
+  }
+}
+
+// o[t, c] = the sum of the row groups' slices, in their order.
+__global__ void scan_sum_slices_kernel(const float* __restrict__ slices, float* __restrict__ o, size_t n, int groups) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float a = slices[i];
+    for (int g = 1; g < groups; ++g) a += slices[(size_t)g * n + i];
+    o[i] = a;
   }
 }
 
@@ -147,17 +163,28 @@ gated_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zf, co
 // state: [slots, heads, dim, vdim] 32-bit; o: [T, ldo] 32-bit; B sequences, sequence b owning the
 // tokens seq_start[b] .. seq_start[b + 1] - 1 of the step.
 // `zq` and `zf` are overwritten with q and f when the step has many tokens per sequence (T > 4 B).
+// `slices` (room for tl_gated_scan_groups(...) * T * ldo floats, or null): with it and such a step the
+// rows of the state are shared out over that many warps per column group, four times the warps to hide
+// the latencies of the sequential walk; ldo must then be the row length of `o` (contiguous rows).
+extern "C" int TL_NAME(tl_gated_scan_groups)(int T, int B, int dim) {
+  if (T <= 4 * B || T < 256) return 1;
+  const int r = (dim + 31) / 32;
+  return r >= 4 ? 4 : r >= 2 ? 2 : 1;
+}
+
 extern "C" int TL_NAME(tl_gated_scan)(float* zq, float* zf, const float* zv, int ld, const float* bias,
                                       const float* low, float* state, float* o, int ldo, const int* seq_start,
                                       const int* seq_slot, int T, int B, int heads, int dim, int vdim,
-                                      cudaStream_t stream) {
+                                      float* slices, cudaStream_t stream) {
   if (B <= 0 || T <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0) return TL_ERR_BAD_ARG;
   if (dim > 32 * SCAN_MAX_R || heads > 65535) return TL_ERR_UNSUPPORTED;
   const int per_block = SCAN_WARPS * SCAN_COLS;
-  dim3 grid(B, heads, (vdim + per_block - 1) / per_block);
+  const int groups = slices != nullptr ? TL_NAME(tl_gated_scan_groups)(T, B, dim) : 1;
+  dim3 grid(B, heads, (vdim + per_block - 1) / per_block * groups);
   if (grid.z > 65535) return TL_ERR_UNSUPPORTED;
-  const int R = (dim + 31) / 32;
+  const int R = ((dim + 31) / 32 + groups - 1) / groups;
+  float* dst = groups > 1 ? slices : o;
   const bool pre = T > 4 * B;
   if (pre) {
     const size_t total = (size_t)T * heads * dim;
@@ -166,13 +193,15 @@ extern "C" int TL_NAME(tl_gated_scan)(float* zq, float* zf, const float* zv, int
                              heads * dim);
     if (rc != 0) return rc;
   }
+  int rc;
 #define SCAN(RR)                                                                                               \
-  return pre ? tl_launch(gated_scan_kernel<RR, true>, grid, dim3(SCAN_WARPS * 32), 0, stream,                  \
-                         (const float*)zq, (const float*)zf, zv, ld, bias, low, state, o, ldo, seq_start,      \
-                         seq_slot, heads, dim, vdim)                                                           \
-             : tl_launch(gated_scan_kernel<RR, false>, grid, dim3(SCAN_WARPS * 32), 0, stream,                 \
-                         (const float*)zq, (const float*)zf, zv, ld, bias, low, state, o, ldo, seq_start,      \
-                         seq_slot, heads, dim, vdim)
+  rc = pre ? tl_launch(gated_scan_kernel<RR, true>, grid, dim3(SCAN_WARPS * 32), 0, stream,                    \
+                       (const float*)zq, (const float*)zf, zv, ld, bias, low, state, dst, ldo, seq_start,      \
+                       seq_slot, heads, dim, vdim, groups, T)                                                  \
+           : tl_launch(gated_scan_kernel<RR, false>, grid, dim3(SCAN_WARPS * 32), 0, stream,                   \
+                       (const float*)zq, (const float*)zf, zv, ld, bias, low, state, dst, ldo, seq_start,      \
+                       seq_slot, heads, dim, vdim, groups, T);                                                 \
+  break
   switch (R) {
     case 1: SCAN(1);
     case 2: SCAN(2);
@@ -184,4 +213,8 @@ extern "C" int TL_NAME(tl_gated_scan)(float* zq, float* zf, const float* zv, int
     default: SCAN(8);
   }
 #undef SCAN
+  if (rc != 0 || groups == 1) return rc;
+  const size_t n = (size_t)T * ldo;
+  const unsigned blocks = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  return tl_launch(scan_sum_slices_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)slices, o, n, groups);
 }

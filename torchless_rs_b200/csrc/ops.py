@@ -133,7 +133,7 @@ class CoreOps:
         self.lib = build.load_library(f"core_{self.suffix}")
         for base in ("tl_embed", "tl_softcap", "tl_advance_step", "tl_regroup_step", "tl_convert", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
                      "tl_gemm_generic", "tl_attn_generic", "tl_pair_embed_add", "tl_branch_norm_add", "tl_poly_norm",
-                     "tl_latent_prep", "tl_headwise_gemm", "tl_latent_attn", "tl_gated_scan"):
+                     "tl_latent_prep", "tl_headwise_gemm", "tl_latent_attn", "tl_gated_scan", "tl_gated_scan_groups"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
             setattr(self, "_" + base, fn)
@@ -463,7 +463,7 @@ class CoreOps:
     # ---- gated linear recurrence ------------------------------------------------------------------
     def gated_scan(self, z: torch.Tensor, bias: torch.Tensor, low: torch.Tensor, state: torch.Tensor,
                    out: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor, heads: int, dim: int,
-                   vdim: int) -> None:
+                   vdim: int, workspace=None) -> None:
         """The recurrence S <- diag(f) S + (1 - f) v^T, o = S^T q over each sequence's tokens of the step,
         from and into `state` [slots, heads, dim, vdim]; `z` [T, 2 heads dim + heads vdim] 32-bit holds the
         projections for q, f and v side by side (for steps of many tokens per sequence the q and f columns
@@ -477,12 +477,21 @@ class CoreOps:
         if z.shape[1] != 2 * hd + heads * vdim or z.stride(1) != 1 or out.shape != (T, heads * vdim) or \
                 bias.numel() != hd or low.numel() != hd or state.shape[1:] != (heads, dim, vdim):
             raise KernelError("gated_scan: sizes do not match")
+        # long steps: the state's rows are shared out over several warps, whose sums are added afterwards
+        groups = self._tl_gated_scan_groups(c_int(T), c_int(seq_slot.numel()), c_int(dim))
+        slices = None
+        if groups > 1:
+            n = groups * T * heads * vdim
+            slices = (workspace.get("scan_slices", (n,), torch.float32) if workspace is not None
+                      else torch.empty(n, dtype=torch.float32, device=z.device))
         _check(self._tl_gated_scan(_ptr(z), _ptr(z[:, hd:]), _ptr(z[:, 2 * hd:]), c_int(z.stride(0)), _ptr(bias),
                                    _ptr(low), _ptr(state), _ptr(out), c_int(out.stride(0)), _ptr(seq_start),
                                    _ptr(seq_slot), c_int(T), c_int(seq_slot.numel()), c_int(heads), c_int(dim),
-                                   c_int(vdim), _stream()), "gated_scan")
+                                   c_int(vdim), _ptr(slices), _stream()), "gated_scan")
         if T > 4 * seq_slot.numel():
             _check(0, "scan_gates")
+        if groups > 1:
+            _check(0, "scan_sum_slices")
 
 
 class SamplingOps:

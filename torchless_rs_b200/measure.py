@@ -292,8 +292,10 @@ def kikopel_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) 
         zz = torch.randn((n_tok, 2 * rh * rd + rh * rv), device=dev)
         state = torch.zeros((seqs, rh, rd, rv), device=dev)
         so = torch.empty((n_tok, rh * rv), device=dev)
+        from .parts.runtime import Workspace as _Ws
+        scan_ws = _Ws(torch.device("cuda"))
         bias, low = torch.zeros(rh * rd, device=dev), torch.full((rh * rd,), 0.5, device=dev)
-        us = _time(lambda: o.gated_scan(zz, bias, low, state, so, start, slot, rh, rd, rv),
+        us = _time(lambda: o.gated_scan(zz, bias, low, state, so, start, slot, rh, rd, rv, workspace=scan_ws),
                    max(2, iters // 8) if n_tok > 64 else iters)
         report("gated_scan", case, us, n_tok * (2 * rh * rd + 2 * rh * rv) * 4.0 + seqs * rh * rd * rv * 8.0,
                4.0 * n_tok * rh * rd * rv)

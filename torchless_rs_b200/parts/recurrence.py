@@ -80,7 +80,8 @@ class GatedLinearRecurrence:
         z = ws.get("scan_in", (T, 2 * H * dim + H * vdim), torch.float32)
         self.matmul(xn, self.w_in, z, ops.MODE_STORE_F32)
         out = ws.get("scan_out", (T, H * vdim), torch.float32)
-        rt.ops.gated_scan(z, self.bias, self.low, self.state, out, batch.seq_start, batch.seq_slot, H, dim, vdim)
+        rt.ops.gated_scan(z, self.bias, self.low, self.state, out, batch.seq_start, batch.seq_slot, H, dim, vdim,
+                          workspace=ws)
         normed = ws.get("scan_normed", (T * H, vdim), rt.act_dtype)
         rt.ops.rmsnorm(out.view(T * H, vdim), self.norm_w, self.eps, normed)
         self.matmul(normed.view(T, H * vdim), self.w_o, residual,
