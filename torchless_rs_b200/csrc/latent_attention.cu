@@ -365,6 +365,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware's approximation (relative error about 2^-22; 0 for x = -inf), as the other
+// tensor-core attention kernels of this package take their exponentials.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -403,32 +410,38 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   __nv_bfloat16* Qt = Qs + wg * 16 * pitch;
   float* Ss = Ss_all + wg * 16 * LM_SPITCH;
-  // the queries of this token's heads: [latent-space part | rotated part], times scale
+  // the queries of this token's heads: [latent-space part | rotated part], times scale; cosines and sines
+  // of the token's angles once per token (they wait in the token's score buffer, which is free until the
+  // first chunk)
   {
     const int half = dims >> 1;
     const int t = t0 + my;
-    for (int idx = tid & (LM_THREADS - 1); idx < 16 * width; idx += LM_THREADS) {
-      const int r = idx / width, d = idx - r * width, h = hg * 16 + r;
-      float v = 0.0f;
-      if (h < heads) {
-        if (d < rank) {
-          v = qa[(size_t)t * ld_qa + (size_t)h * qa_head + d];
-        } else {
-          const float* src = q + (size_t)t * ldq + (size_t)h * q_head + q_off;
-          const int j = d - rank;
-          if (j < dims) {
-            const int i = j < half ? j : j - half;
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i], &sn, &cs);
-            const float u = src[i], w = src[i + half];
-            v = j < half ? u * cs - w * sn : w * cs + u * sn;
-          } else {
-            v = src[j];
-          }
-        }
-        v *= scale;
+    const int tl = tid & (LM_THREADS - 1);
+    float2* cs_s = reinterpret_cast<float2*>(Ss);            // [half] <= 16 * LM_SPITCH / 2 (the launcher checks)
+    for (int i = tl; i < half; i += LM_THREADS) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      cs_s[i] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    const float qscale = scale * 1.4426950408889634f;      // log2(e): the softmax below works in base 2
+    for (int r = 0; r < 16; ++r) {
+      const int h = hg * 16 + r;
+      __nv_bfloat16* dst = Qt + r * pitch;
+      if (h >= heads) {
+        for (int d = tl; d < width; d += LM_THREADS) dst[d] = __float2bfloat16_rn(0.0f);
+        continue;
       }
-      Qt[r * pitch + d] = __float2bfloat16_rn(v);
+      const float* qsrc = qa + (size_t)t * ld_qa + (size_t)h * qa_head;
+      for (int d = tl; d < rank; d += LM_THREADS) dst[d] = __float2bfloat16_rn(qsrc[d] * qscale);
+      const float* src = q + (size_t)t * ldq + (size_t)h * q_head + q_off;
+      for (int i = tl; i < half; i += LM_THREADS) {
+        const float2 c = cs_s[i];
+        const float u = src[i], w = src[i + half];
+        dst[rank + i] = __float2bfloat16_rn((u * c.x - w * c.y) * qscale);
+        dst[rank + half + i] = __float2bfloat16_rn((w * c.x + u * c.y) * qscale);
+      }
+      for (int j = dims + tl; j < rot; j += LM_THREADS) dst[rank + j] = __float2bfloat16_rn(src[j] * qscale);
     }
   }
   float acc[2 * NTP][4];
@@ -457,14 +470,34 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
         rowp[tid] = i <= p_last ? pages + ((size_t)table[i / TL_PAGE] * TL_PAGE + (i % TL_PAGE)) * width : nullptr;
       }
       __syncthreads();
-      for (int idx = tid; idx < LM_KC * vecs; idx += LM_THREADS * TB) {
-        const int r = idx / vecs, v = idx - r * vecs;
-        __nv_bfloat16* dst = Ks + r * pitch + v * 8;
-        if (rowp[r] != nullptr) {
-          const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(rowp[r] + v * 8) : "memory");
+      if (TB == 1) {
+        // few threads: consecutive threads take consecutive 16-byte pieces
+        for (int idx = tid; idx < LM_KC * vecs; idx += LM_THREADS) {
+          const int r = idx / vecs, v = idx - r * vecs;
+          __nv_bfloat16* dst = Ks + r * pitch + v * 8;
+          if (rowp[r] != nullptr) {
+            const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(rowp[r] + v * 8) : "memory");
+          } else {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      } else {
+        // a fixed row per thread (2 TB threads share a row, 32 TB bytes in a run), so that no index is
+        // divided (measured at four tokens a block: 747 us against 838 us with the loop above and 823 us
+        // with a warp per row)
+        constexpr int PER_ROW = LM_THREADS * TB / LM_KC;
+        const int r = tid / PER_ROW;
+        const __nv_bfloat16* src = rowp[r];
+        __nv_bfloat16* dst = Ks + r * pitch;
+        if (src != nullptr) {
+          for (int v = tid % PER_ROW; v < vecs; v += PER_ROW) {
+            const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst + v * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(src + v * 8) : "memory");
+          }
         } else {
-          *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+          for (int v = tid % PER_ROW; v < vecs; v += PER_ROW)
+            *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
       asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
@@ -474,6 +507,8 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
         float sc[2][4] = {};
         const __nv_bfloat16* qrow = Qt + ((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (lane >> 4) * 8;
         const __nv_bfloat16* krow = Ks + (warp * 16 + (lane >> 4) * 8 + (lane & 7)) * pitch + ((lane >> 3) & 1) * 8;
+        // (unrolled so that the loads of the next steps are issued before this step's products wait for theirs)
+#pragma unroll 4
         for (int ks = 0; ks < width; ks += 16) {
           uint32_t a[4], b[4];
           ldsm_x4(a, qrow + ks);
@@ -514,13 +549,13 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
         // The first chunk of a token's range holds a key it sees, so the maximum is finite from then on; a
         // later chunk in which this token sees no key (only a neighbour does) leaves everything as it is.
         const float m_new = fmaxf(m_run[r], cmax[r]);
-        alpha[r] = m_new == -INFINITY ? 1.0f : expf(m_run[r] - m_new);      // 0 at the first chunk
+        alpha[r] = m_new == -INFINITY ? 1.0f : fast_exp2(m_run[r] - m_new);      // 0 at the first chunk
         float sum = 0.0f;
 #pragma unroll
         for (int kk = 0; kk < LM_KC / 16; ++kk)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            s[r][kk][e] = m_new == -INFINITY ? 0.0f : expf(s[r][kk][e] - m_new);   // 0 for keys not seen
+            s[r][kk][e] = m_new == -INFINITY ? 0.0f : fast_exp2(s[r][kk][e] - m_new);   // 0 for keys not seen
             sum += s[r][kk][e];
           }
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -593,27 +628,29 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
   }
 }
 
-// Merges the parts of a token's keys: out = sum_s w_s O_s / sum_s w_s l_s with w_s = exp(m_s - max m).
-__global__ void latent_attn_merge_kernel(const float* __restrict__ part, float* __restrict__ o, int heads, int hpad,
-                                         int rank, int splits) {
+// Merges the parts of a token's keys: out = sum_s w_s O_s / sum_s w_s l_s with w_s = 2^(m_s - max m)
+// (the maxima are those of the scores times log2(e)).
+__global__ void __launch_bounds__(128)
+latent_attn_merge_kernel(const float* __restrict__ part, float* __restrict__ o, int heads, int hpad, int rank,
+                         int splits) {
+  __shared__ float w_s[64];      // the parts' weights (at most 64 parts), then divided by their sum
+  __shared__ float scratch[33];
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, h = blockIdx.y;
-  const float* src = part + ((size_t)t * hpad + h) * splits * (size_t)(rank + 2);
-  float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, src[(size_t)s * (rank + 2) + rank]);
-  float l = 0.0f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = src[(size_t)s * (rank + 2) + rank];
-    if (ms != -INFINITY) l += expf(ms - m) * src[(size_t)s * (rank + 2) + rank + 1];
-  }
+  const size_t stride = (size_t)(rank + 2);
+  const float* src = part + ((size_t)t * hpad + h) * splits * stride;
+  const float ms = (int)threadIdx.x < splits ? src[threadIdx.x * stride + rank] : -INFINITY;
+  const float m = block_max(ms, scratch);
+  const float w = ms != -INFINITY ? exp2f(ms - m) : 0.0f;
+  const float l = block_sum((int)threadIdx.x < splits ? w * src[threadIdx.x * stride + rank + 1] : 0.0f, scratch);
+  if ((int)threadIdx.x < splits) w_s[threadIdx.x] = w / l;
+  __syncthreads();
   for (int d = threadIdx.x; d < rank; d += blockDim.x) {
     float a = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = src[(size_t)s * (rank + 2) + rank];
-      if (ms != -INFINITY) a = fmaf(expf(ms - m), src[(size_t)s * (rank + 2) + d], a);
-    }
-    o[((size_t)t * heads + h) * rank + d] = a / l;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) a = fmaf(w_s[s], src[(size_t)s * stride + d], a);
+    o[((size_t)t * heads + h) * rank + d] = a;
   }
 }
 
@@ -622,7 +659,7 @@ __global__ void latent_attn_merge_kernel(const float* __restrict__ part, float* 
 extern "C" int tl_latent_attn_plan(int T, int heads, int rank, int rot, int max_keys, int num_sms,
                                    long long* part_floats) {
   *part_floats = 0;
-  if (rank % 16 || rot % 16 || rank > 512 || rank <= 0) return 0;     // the CUDA-core kernel
+  if (rank % 16 || rot % 16 || rank > 512 || rank <= 0 || rot > 1024) return 0;     // the CUDA-core kernel
   const size_t smem = (size_t)(16 + LM_KC) * (rank + rot + 8) * 2 + 16 * LM_SPITCH * 4 + LM_KC * 8;
   if (smem > 200 * 1024) return 0;      // (one token a block; lm_smem_bytes(1, ...) below)
   const int groups = (heads + 15) / 16;
@@ -649,7 +686,7 @@ extern "C" int tl_latent_attn_mma(const float* qa, int ld_qa, int qa_head, const
                                   int table_stride, const float* inv_freq, int T, int heads, int rank, int rot,
                                   int dims, int window, float scale, int splits, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (rank % 16 || rot % 16 || rank > 512 || rank <= 0 || dims > rot || (dims & 1) || splits < 1 ||
+  if (rank % 16 || rot % 16 || rank > 512 || rank <= 0 || dims > rot || (dims & 1) || rot > 1024 || splits < 1 ||
       (splits > 1 && part == nullptr))
     return TL_ERR_UNSUPPORTED;
   const int groups = (heads + 15) / 16;
