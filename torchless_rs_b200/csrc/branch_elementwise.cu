@@ -75,7 +75,7 @@ extern "C" int TL_NAME(tl_pair_embed_add)(const int* tokens, const int* token_fr
 // x[r, :] += m * g * y[r, :] / sqrt(mean(y[r, :]^2) + eps); g is one number.  With `xb` given,
 // xb[r, :] = the new x[r, :] in the activation type.  y: [rows, H] 32-bit, row stride ldy.
 // ---------------------------------------------------------------------------
-#define BRANCH_KEEP 8
+#define BRANCH_KEEP 16
 __global__ void branch_norm_add_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ gain,
                                        float m, float eps, float* __restrict__ x, act_t* __restrict__ xb,
                                        int H) {
@@ -133,7 +133,7 @@ extern "C" int TL_NAME(tl_branch_norm_add)(const float* y, int ldy, const float*
 // out[r, :] = a N(z) + b N(z^2) + c N(z^3) + e over a row z of F numbers, powers taken element by
 // element, N(u) = u / sqrt(mean(u^2) + eps); coeff = (a, b, c, e).  z 32-bit with row stride ldz.
 // ---------------------------------------------------------------------------
-#define POLY_KEEP 24
+#define POLY_KEEP 32
 __global__ void poly_norm_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ coeff,
                                  float eps, act_t* __restrict__ out, int F) {
   __shared__ float scratch[33];
