@@ -296,12 +296,13 @@ def design_arm(args) -> int:
            "decode_context": ctx, "steps": args.steps, "warmup": args.warmup}
     clocks = ClockSampler()
     clocks.start()
-    t0 = clocks.mark()
+    t0 = None
     greedy = SamplingParams.greedy()
     for name, cfg in (("kikopel", measure.kikopel_config(size, L)), ("mistral", measure.mistral_like(size, L))):
         model = tl.from_random(config_from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=B * (ctx + 64),
                                max_batch=B, max_seq_len=ctx + 64)
         eng = model.engine
+        t0 = t0 or clocks.mark()      # the clocks are read from the first timed region on
         pre_ms, pre_all = prefill_timed(model, T, repeats=3)
         # decode: every sequence is prefilled to the context first, then K steps are timed on the device
         toks = [[(13 * i + 7 * b + 1) % eng.vocab_size for i in range(ctx - args.steps - args.warmup)] for b in range(B)]

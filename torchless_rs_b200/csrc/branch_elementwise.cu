@@ -75,7 +75,7 @@ extern "C" int TL_NAME(tl_pair_embed_add)(const int* tokens, const int* token_fr
 // x[r, :] += m * g * y[r, :] / sqrt(mean(y[r, :]^2) + eps); g is one number.  With `xb` given,
 // xb[r, :] = the new x[r, :] in the activation type.  y: [rows, H] 32-bit, row stride ldy.
 // ---------------------------------------------------------------------------
-#define BRANCH_KEEP 16
+#define BRANCH_KEEP 8
 __global__ void branch_norm_add_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ gain,
                                        float m, float eps, float* __restrict__ x, act_t* __restrict__ xb,
                                        int H) {
@@ -124,7 +124,7 @@ extern "C" int TL_NAME(tl_branch_norm_add)(const float* y, int ldy, const float*
                                            float* x, void* xb, int rows, int H, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || gain == nullptr) return TL_ERR_BAD_ARG;
-  const int threads = H <= 1024 ? 128 : H <= 4096 ? 256 : 512;
+  const int threads = H <= 1024 ? 128 : H <= 2048 ? 256 : 512;      // 8 values a thread up to 4096
   return tl_launch(branch_norm_add_kernel, dim3(rows), dim3(threads), 0, stream, y, ldy, gain, m, eps, x,
                    (act_t*)xb, H);
 }
@@ -189,6 +189,6 @@ extern "C" int TL_NAME(tl_poly_norm)(const float* z, int ldz, const float* coeff
                                      int F, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (F <= 0 || coeff == nullptr) return TL_ERR_BAD_ARG;
-  const int threads = F <= 2048 ? 128 : F <= 6144 ? 256 : 512;
+  const int threads = F <= 2048 ? 128 : F <= 4096 ? 256 : 512;
   return tl_launch(poly_norm_kernel, dim3(rows), dim3(threads), 0, stream, z, ldz, coeff, eps, (act_t*)out, F);
 }
