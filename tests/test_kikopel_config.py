@@ -146,3 +146,22 @@ def test_plain_attention_of_one_head_is_ordinary_attention():
         a = np.exp(s - s.max()); a /= a.sum()
         out[i] = sum(a[t] * v[j] for t, j in enumerate(js))
     assert np.allclose(got, (out / (1 + np.exp(-(h @ w["g"].T)))) @ w["o"].T)
+
+
+def test_a_folder_may_store_the_second_gain_of_a_layer_without_feed_forward(tmp_path):
+    from safetensors.torch import save_file
+    from torchless_rs_b200.weights.loader import load_checked
+    import json, os
+    cfg = CONFIGS["Q"]                                   # its layer 1 has no feed-forward
+    w = make_weights(cfg, 2, torch.float32)
+    assert "l1.norm2" not in w
+    w["l1.norm2"] = torch.tensor(1.25)
+    save_file({k: v.contiguous() for k, v in w.items()}, os.path.join(tmp_path, "model.safetensors"))
+    exp = expected_tensors(tl.config_from_dict(cfg).model_spec())
+    got, src = load_checked(str(tmp_path), exp, torch.float32)
+    src.close()
+    assert exp["l1.norm2"].optional and "l1.norm2" in got
+    w["l1.norm3"] = torch.tensor(1.0)                    # any other name is still refused
+    save_file({k: v.contiguous() for k, v in w.items()}, os.path.join(tmp_path, "model.safetensors"))
+    with pytest.raises(tl.WeightsMismatchError, match="norm3"):
+        load_checked(str(tmp_path), exp, torch.float32)

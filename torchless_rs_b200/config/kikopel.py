@@ -176,9 +176,12 @@ class KikopelConfig:
                 block = "branchnorm"
                 ff = PartSpec("polynorm", {"hidden_size": self.width, "intermediate_size": l.ff, "eps": self.eps})
                 norms = {"mixer_out_norm": norm, "feed_forward_out_norm": norm}
+            # a layer without a feed-forward needs no second norm; a folder that stores its gain all the
+            # same is accepted
+            unused = {} if l.ff is not None else {LAYER_TENSOR_NAMES["feed_forward_out_norm"]: ()}
             layers.append(LayerSpec(prefix=f"l{i}", block=PartSpec(block, {"residual_mult": self.residual_mult}),
                                     mixer=mixer, feed_forward=ff, norms=norms, names=LAYER_TENSOR_NAMES,
-                                    position=position))
+                                    position=position, unused_tensors=unused))
         addend = None
         if self.bigram is not None:
             addend = PartSpec("pair_hash", {"name": "bigram", "hidden_size": self.width, "vocab_size": self.vocab,

@@ -41,6 +41,9 @@ class LayerSpec:
     names: Mapping[str, str]
     position: Optional[PartSpec] = None
     cache_from: Optional[int] = None
+    # Tensors under `prefix` that a folder may hold although no part of the layer uses them (name under
+    # the prefix -> shape): they are accepted if present and never asked for.
+    unused_tensors: Mapping[str, tuple] = field(default_factory=dict)
 
     def tensor_prefix(self, role: str) -> str:
         from .errors import ConfigError

@@ -133,10 +133,11 @@ extern "C" int TL_NAME(tl_branch_norm_add)(const float* y, int ldy, const float*
 // out[r, :] = a N(z) + b N(z^2) + c N(z^3) + e over a row z of F numbers, powers taken element by
 // element, N(u) = u / sqrt(mean(u^2) + eps); coeff = (a, b, c, e).  z 32-bit with row stride ldz.
 // ---------------------------------------------------------------------------
-#define POLY_KEEP 32
+// KEEP: values a thread keeps in registers (the row is read once if it fits KEEP * threads).
+template <int POLY_KEEP>
 __global__ void poly_norm_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ coeff,
                                  float eps, act_t* __restrict__ out, int F) {
-  __shared__ float scratch[33];
+  __shared__ float sums[3][33];
   pdl_wait();
   pdl_launch_dependents();
   const int r = blockIdx.x;
@@ -163,32 +164,58 @@ __global__ void poly_norm_kernel(const float* __restrict__ z, int ldz, const flo
       s6 = fmaf(v3, v3, s6);
     }
   }
-  s2 = block_sum(s2, scratch);
-  s4 = block_sum(s4, scratch);
-  s6 = block_sum(s6, scratch);
+  // the three sums in one pass through shared memory
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    s2 = warp_sum(s2); s4 = warp_sum(s4); s6 = warp_sum(s6);
+    if (lane == 0) { sums[0][warp] = s2; sums[1][warp] = s4; sums[2][warp] = s6; }
+    __syncthreads();
+    if (warp < 3) {
+      float t = lane < nwarps ? sums[warp][lane] : 0.0f;
+      t = warp_sum(t);
+      if (lane == 0) sums[warp][32] = t;
+    }
+    __syncthreads();
+    s2 = sums[0][32]; s4 = sums[1][32]; s6 = sums[2][32];
+  }
   const float r1 = sqrtf(s2 / (float)F + eps), r2 = sqrtf(s4 / (float)F + eps), r3 = sqrtf(s6 / (float)F + eps);
+#if TL_DTYPE == 0
+  // the 32-bit path divides every value, as its other norms do
+#define POLY_N(v, r) ((v) / (r))
   const float a = coeff[0], b = coeff[1], c = coeff[2], e = coeff[3];
+#else
+  // rounded to bfloat16 afterwards: one division per row and power, folded into the coefficients
+#define POLY_N(v, r) (v)
+  const float a = coeff[0] / r1, b = coeff[1] / r2, c = coeff[2] / r3, e = coeff[3];
+#endif
   if (fits) {
 #pragma unroll
     for (int j = 0; j < POLY_KEEP; ++j) {
       const int i = threadIdx.x + j * blockDim.x;
       if (i < F) {
         const float v = keep[j], v2 = v * v, v3 = v2 * v;
-        out[(size_t)r * F + i] = from_f32<act_t>(a * (v / r1) + b * (v2 / r2) + c * (v3 / r3) + e);
+        out[(size_t)r * F + i] = from_f32<act_t>(a * POLY_N(v, r1) + b * POLY_N(v2, r2) + c * POLY_N(v3, r3) + e);
       }
     }
   } else {
     for (int i = threadIdx.x; i < F; i += blockDim.x) {
       const float v = zr[i], v2 = v * v, v3 = v2 * v;
-      out[(size_t)r * F + i] = from_f32<act_t>(a * (v / r1) + b * (v2 / r2) + c * (v3 / r3) + e);
+      out[(size_t)r * F + i] = from_f32<act_t>(a * POLY_N(v, r1) + b * POLY_N(v2, r2) + c * POLY_N(v3, r3) + e);
     }
   }
 }
+
+#undef POLY_N
 
 extern "C" int TL_NAME(tl_poly_norm)(const float* z, int ldz, const float* coeff, float eps, void* out, int rows,
                                      int F, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (F <= 0 || coeff == nullptr) return TL_ERR_BAD_ARG;
-  const int threads = F <= 2048 ? 128 : F <= 4096 ? 256 : 512;
-  return tl_launch(poly_norm_kernel, dim3(rows), dim3(threads), 0, stream, z, ldz, coeff, eps, (act_t*)out, F);
+  const int threads = F <= 1024 ? 128 : F <= 4096 ? 256 : 512;
+  const int per = (F + threads - 1) / threads;
+  if (per <= 8)
+    return tl_launch(poly_norm_kernel<8>, dim3(rows), dim3(threads), 0, stream, z, ldz, coeff, eps, (act_t*)out, F);
+  if (per <= 16)
+    return tl_launch(poly_norm_kernel<16>, dim3(rows), dim3(threads), 0, stream, z, ldz, coeff, eps, (act_t*)out, F);
+  return tl_launch(poly_norm_kernel<32>, dim3(rows), dim3(threads), 0, stream, z, ldz, coeff, eps, (act_t*)out, F);
 }

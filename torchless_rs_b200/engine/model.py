@@ -44,6 +44,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
                 [("mixer", layer.mixer, "mixer"), ("feed_forward", layer.feed_forward, "feed_forward")] +
                 [("norm", ps, role) for role, ps in layer.norms.items()]):
             out.update(lookup(table, ps.kind).expected_tensors(_own(ps, layer), layer.tensor_prefix(role)))
+        for name, shape in layer.unused_tensors.items():
+            out.setdefault(f"{layer.prefix}.{name}", TensorSpec(tuple(shape), optional=True))
     out.update(lookup("norm", spec.final_norm.kind).expected_tensors(spec.final_norm,
                                                                      spec.final_norm_prefix))
     if not spec.tie_head_to_embedding:
