@@ -38,7 +38,7 @@ def with_ff(layer, ff):
     return {**layer, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
 
 
-def config(width, vocab, layers, eps=1e-5, mult=0.7, scale=1.0, bigram=(37, 5, 3)):
+def config(width, vocab, layers, eps=1e-5, mult=0.6, scale=1.0, bigram=(37, 5, 3)):
     emb = {"scale": scale}
     if bigram:
         emb["bigram"] = {"buckets": bigram[0], "mul_prev": bigram[1], "mul_cur": bigram[2]}

@@ -188,11 +188,11 @@ def kikopel_config(size: str, layers: int) -> dict:
     att = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": z["ff"]},
            "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"],
                      "q_rank": z["q_rank"], "kv_rank": z["kv_rank"], "mask": {"size": z["window"]},
-                     "rot": {"base": 1e6, "dims": z["rot"]}, "scale": 1.0 / math.sqrt(z["dim"] + z["rot"])}}
+                     "rot": {"base": 500000.0, "dims": z["rot"]}, "scale": 1.0 / math.sqrt(z["dim"] + z["rot"])}}
     rec = {"type": "hgrn2", "mlp": {"kind": "dense", "ff": z["ff"]},
            "mixer": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"]}}
     return {"architecture": "Kikopel", "width": z["width"], "vocab": z["vocab"], "norm": {"eps": 1e-5},
-            "residual_mult": 0.7, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+            "residual_mult": 0.6, "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 131}},
             "layers": [rec if i % 4 == 1 else att for i in range(layers)], "max_position_embeddings": 32768}
 
 
@@ -233,7 +233,7 @@ def kikopel_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) 
                      "bound": "memory" if t_mem >= t_fl else "tensor"})
         print(f"{name:28s} {case:22s} {us:10.2f} us   {frac:7.4f} of the roofline ({rows[-1]['bound']})", file=file)
 
-    inv = torch.tensor([1e6 ** (-2.0 * i / rot) for i in range(rot // 2)], device=dev)
+    inv = torch.tensor([500000.0 ** (-2.0 * i / rot) for i in range(rot // 2)], device=dev)
     for case, n_tok, seqs, past in ((f"prompt {T}", T, 1, 0), (f"decode {B} x {ctx}", B, B, ctx - 1)):
         per = n_tok // seqs
         pages_per = (past + per + 63) // 64
@@ -303,7 +303,7 @@ def kikopel_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) 
         y, x = torch.randn((n_tok, W), device=dev), torch.randn((n_tok, W), device=dev)
         xb = torch.empty((n_tok, W), device=dev, dtype=bf)
         g1 = torch.ones(1, device=dev)
-        us = _time(lambda: o.branch_norm_add(y, g1, 0.7, 1e-5, x, xb), iters)
+        us = _time(lambda: o.branch_norm_add(y, g1, 0.6, 1e-5, x, xb), iters)
         report("branch_norm_add", case, us, n_tok * W * 14.0, 0.0)
         zf = torch.randn((n_tok, z["ff"]), device=dev)
         af = torch.empty((n_tok, z["ff"]), device=dev, dtype=bf)
