@@ -61,10 +61,10 @@ CONFIGS = {
         with_ff(latent(4, 8, 24, 6, 56, 20, window=1), 64),
     ], eps=3e-5, mult=1.0, scale=1.0, bigram=None),
     # sizes that the tensor-core products take (multiples of 8 and more), a window across pages
-    "R": config(256, 512, [
-        with_ff(latent(4, 32, 32, 48, 64, 96, window=130, base=1000000.0), 384),
+    "R": config(256, 520, [
+        with_ff(latent(4, 32, 32, 48, 64, 96, window=130, base=250000.0), 448),
         with_ff(recur(4, 64, 32), 256),
-        with_ff(latent(4, 32, 32, 48, 64, 96, window=64), 384),
+        with_ff(latent(4, 32, 32, 48, 64, 96, window=64), 448),
     ], eps=1e-5, mult=0.8, scale=4.0, bigram=(1021, 131, 17)),
 }
 

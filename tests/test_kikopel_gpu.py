@@ -317,7 +317,7 @@ def test_latent_attention_of_a_long_packed_step(window, heads, rank, rot):
     assert worst <= 2e-2, f"{worst:.3e}"
 
 
-@pytest.mark.parametrize("heads,dim,vdim", [(2, 16, 8), (1, 40, 20), (3, 70, 33), (2, 128, 64)])
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 16, 8), (1, 40, 20), (3, 70, 33), (2, 128, 64), (1, 300, 12)])
 def test_gated_scan_carries_its_state(heads, dim, vdim):
     """The recurrence over a batch of two sequences, whole and in pieces down to one token, from
     the state that the piece before left in the sequence's slot; a slot's state that is zeroed

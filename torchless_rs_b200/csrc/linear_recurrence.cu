@@ -15,7 +15,7 @@
 
 #define SCAN_COLS 4          // columns per warp (warp_sum4 is written for 4)
 #define SCAN_WARPS 4         // warps per block
-#define SCAN_MAX_R 8         // rows per lane: dim <= 256
+#define SCAN_MAX_R 8         // rows per lane; wider states are shared out over several warps
 
 // The gates of all tokens at once, in place: zq <- silu(zq), zf <- low + (1 - low) sigmoid(zf + bias).
 // For steps of many tokens per sequence, so that the sequential walk below is left with the
@@ -163,13 +163,16 @@ __global__ void scan_sum_slices_kernel(const float* __restrict__ slices, float* 
 // state: [slots, heads, dim, vdim] 32-bit; o: [T, ldo] 32-bit; B sequences, sequence b owning the
 // tokens seq_start[b] .. seq_start[b + 1] - 1 of the step.
 // `zq` and `zf` are overwritten with q and f when the step has many tokens per sequence (T > 4 B).
-// `slices` (room for tl_gated_scan_groups(...) * T * ldo floats, or null): with it and such a step the
-// rows of the state are shared out over that many warps per column group, four times the warps to hide
-// the latencies of the sequential walk; ldo must then be the row length of `o` (contiguous rows).
+// `slices` (room for tl_gated_scan_groups(...) * T * ldo floats, or null): with it the rows of the state
+// are shared out over that many warps per column group, for long steps (up to four times the warps to
+// hide the latencies of the sequential walk) and for states of more than 256 rows; ldo must then be the
+// row length of `o` (contiguous rows).
 extern "C" int TL_NAME(tl_gated_scan_groups)(int T, int B, int dim) {
-  if (T <= 4 * B || T < 256) return 1;
   const int r = (dim + 31) / 32;
-  return r >= 4 ? 4 : r >= 2 ? 2 : 1;
+  const int need = (r + SCAN_MAX_R - 1) / SCAN_MAX_R;      // a lane holds at most SCAN_MAX_R rows
+  if (T <= 4 * B || T < 256) return need;
+  const int fast = r >= 4 ? 4 : r >= 2 ? 2 : 1;
+  return fast > need ? fast : need;
 }
 
 extern "C" int TL_NAME(tl_gated_scan)(float* zq, float* zf, const float* zv, int ld, const float* bias,
@@ -178,9 +181,10 @@ extern "C" int TL_NAME(tl_gated_scan)(float* zq, float* zf, const float* zv, int
                                       float* slices, cudaStream_t stream) {
   if (B <= 0 || T <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0) return TL_ERR_BAD_ARG;
-  if (dim > 32 * SCAN_MAX_R || heads > 65535) return TL_ERR_UNSUPPORTED;
+  if (heads > 65535) return TL_ERR_UNSUPPORTED;
   const int per_block = SCAN_WARPS * SCAN_COLS;
   const int groups = slices != nullptr ? TL_NAME(tl_gated_scan_groups)(T, B, dim) : 1;
+  if (((dim + 31) / 32 + groups - 1) / groups > SCAN_MAX_R) return TL_ERR_UNSUPPORTED;   // (no slices given)
   dim3 grid(B, heads, (vdim + per_block - 1) / per_block * groups);
   if (grid.z > 65535) return TL_ERR_UNSUPPORTED;
   const int R = ((dim + 31) / 32 + groups - 1) / groups;
