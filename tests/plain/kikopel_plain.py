@@ -12,8 +12,6 @@ down-projection.  Arrays are float64 by default, so this is also the oracle for 
 budgets."""
 from __future__ import annotations
 
-import math
-
 import numpy as np
 
 

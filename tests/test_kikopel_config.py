@@ -151,7 +151,7 @@ def test_plain_attention_of_one_head_is_ordinary_attention():
 def test_a_folder_may_store_the_second_gain_of_a_layer_without_feed_forward(tmp_path):
     from safetensors.torch import save_file
     from torchless_rs_b200.weights.loader import load_checked
-    import json, os
+    import os
     cfg = CONFIGS["Q"]                                   # its layer 1 has no feed-forward
     w = make_weights(cfg, 2, torch.float32)
     assert "l1.norm2" not in w

@@ -5,7 +5,6 @@ command line; then each kernel alone on inputs made so that a wrong window edge,
 key or a lost state shows."""
 import json
 import os
-import shutil
 import subprocess
 import sys
 
@@ -396,7 +395,7 @@ def test_pair_hash_embedding_and_its_remembered_token(dtype):
     x = run([seqs[0][:5], seqs[1][:3], seqs[2]], [0, 0, 0])
     assert np.array_equal(x, np.concatenate([rows(seqs[0], 0, 5), rows(seqs[1], 0, 3), rows(seqs[2], 0, 1)]))
     assert last[slots, 0].tolist() == [seqs[0][4], seqs[1][2], seqs[2][0]] and int(last[1, 0]) == -5
-    slots, keep = slots[:2], None
+    slots = slots[:2]
     x = run([seqs[0][5:8], seqs[1][3:]], [5, 3])
     assert np.array_equal(x, np.concatenate([rows(seqs[0], 5, 8), rows(seqs[1], 3, 4)]))
     slots = slots[:1]

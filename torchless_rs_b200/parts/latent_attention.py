@@ -14,7 +14,7 @@ The three projections of h (W_dq, W_dkv, W_g) are one stacked product."""
 from __future__ import annotations
 
 import math
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 
