@@ -425,23 +425,52 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
     }
     __syncthreads();
     const float qscale = scale * 1.4426950408889634f;      // log2(e): the softmax below works in base 2
-    for (int r = 0; r < 16; ++r) {
-      const int h = hg * 16 + r;
-      __nv_bfloat16* dst = Qt + r * pitch;
-      if (h >= heads) {
-        for (int d = tl; d < width; d += LM_THREADS) dst[d] = __float2bfloat16_rn(0.0f);
-        continue;
+    // the latent-space parts of four heads at a time: their loads are all issued before the first is used
+    // (one after the other they cost a block of one chunk some twenty microseconds)
+    for (int r0 = 0; r0 < 16; r0 += 4) {
+      float v[4][4];                                   // rank <= 512: at most 4 values a thread and head
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int h = hg * 16 + r0 + j;
+        const float* qsrc = qa + (size_t)t * ld_qa + (size_t)(h < heads ? h : 0) * qa_head;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int d = tl + k * LM_THREADS;
+          v[j][k] = (h < heads && d < rank) ? qsrc[d] : 0.0f;
+        }
       }
-      const float* qsrc = qa + (size_t)t * ld_qa + (size_t)h * qa_head;
-      for (int d = tl; d < rank; d += LM_THREADS) dst[d] = __float2bfloat16_rn(qsrc[d] * qscale);
-      const float* src = q + (size_t)t * ldq + (size_t)h * q_head + q_off;
-      for (int i = tl; i < half; i += LM_THREADS) {
-        const float2 c = cs_s[i];
-        const float u = src[i], w = src[i + half];
-        dst[rank + i] = __float2bfloat16_rn((u * c.x - w * c.y) * qscale);
-        dst[rank + half + i] = __float2bfloat16_rn((w * c.x + u * c.y) * qscale);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int d = tl + k * LM_THREADS;
+          if (d < rank) Qt[(r0 + j) * pitch + d] = __float2bfloat16_rn(v[j][k] * qscale);
+        }
+    }
+    // the parts to rotate: a thread takes one pair of entries of all 16 heads, loads first
+    for (int i = tl; i < half; i += LM_THREADS) {
+      float u[16], w[16];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const int h = hg * 16 + r;
+        const float* src = q + (size_t)t * ldq + (size_t)(h < heads ? h : 0) * q_head + q_off;
+        u[r] = h < heads ? src[i] : 0.0f;
+        w[r] = h < heads ? src[i + half] : 0.0f;
       }
-      for (int j = dims + tl; j < rot; j += LM_THREADS) dst[rank + j] = __float2bfloat16_rn(src[j] * qscale);
+      const float2 c = cs_s[i];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        Qt[r * pitch + rank + i] = __float2bfloat16_rn((u[r] * c.x - w[r] * c.y) * qscale);
+        Qt[r * pitch + rank + half + i] = __float2bfloat16_rn((w[r] * c.x + u[r] * c.y) * qscale);
+      }
+    }
+    for (int j = dims + tl; j < rot; j += LM_THREADS) {      // entries that pass unrotated
+#pragma unroll
+      for (int r = 0; r < 16; ++r) {
+        const int h = hg * 16 + r;
+        const float x = h < heads ? q[(size_t)t * ldq + (size_t)h * q_head + q_off + j] : 0.0f;
+        Qt[r * pitch + rank + j] = __float2bfloat16_rn(x * qscale);
+      }
     }
   }
   float acc[2 * NTP][4];
@@ -471,15 +500,18 @@ latent_attn_mma_kernel(const float* __restrict__ qa, int ld_qa, int qa_head, con
       }
       __syncthreads();
       if (TB == 1) {
-        // few threads: consecutive threads take consecutive 16-byte pieces
-        for (int idx = tid; idx < LM_KC * vecs; idx += LM_THREADS) {
-          const int r = idx / vecs, v = idx - r * vecs;
-          __nv_bfloat16* dst = Ks + r * pitch + v * 8;
-          if (rowp[r] != nullptr) {
-            const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(rowp[r] + v * 8) : "memory");
+        // a warp copies whole rows, 512 bytes an instruction (no index is divided: with one warp per
+        // scheduler every instruction counts)
+        for (int r = tid >> 5; r < LM_KC; r += LM_THREADS / 32) {
+          const __nv_bfloat16* src = rowp[r];
+          __nv_bfloat16* dst = Ks + r * pitch;
+          if (src != nullptr) {
+            for (int v = lane; v < vecs; v += 32) {
+              const uint32_t d32 = (uint32_t)__cvta_generic_to_shared(dst + v * 8);
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d32), "l"(src + v * 8) : "memory");
+            }
           } else {
-            *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+            for (int v = lane; v < vecs; v += 32) *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(0u, 0u, 0u, 0u);
           }
         }
       } else {
@@ -666,8 +698,8 @@ extern "C" int tl_latent_attn_plan(int T, int heads, int rank, int rot, int max_
   const long long blocks = (long long)T * groups;
   int splits = 1;
   const int chunks = (max_keys + LM_KC - 1) / LM_KC;
-  if (blocks < 2LL * num_sms) {
-    splits = (int)((2LL * num_sms + blocks - 1) / blocks);
+  if (blocks < 1LL * num_sms) {
+    splits = (int)((1LL * num_sms + blocks - 1) / blocks);
     if (splits > chunks) splits = chunks;
     if (splits > 64) splits = 64;
     if (splits < 1) splits = 1;
