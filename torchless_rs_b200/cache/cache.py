@@ -8,11 +8,12 @@ advances (src/model/mod.rs:93).  Here many sequences live at once:
 * a *slot* stands for one sequence; it records the sequence's length and is given
   back when the sequence ends, then used again;
 * layers whose mixers ask for the same thing form a *group* with storage of its own.
-  A paged group holds keys and values in pages of `PAGE` positions,
-  [layers, 2, pages, kv_heads, PAGE * head_dim] (keys as [PAGE, head_dim], values
-  transposed as [head_dim, PAGE]), and a table from (slot, position //
-  PAGE) to a page.  A group with a window gives pages back as soon as every position
-  in them has left the window of the sequence's next position;
+  A paged group holds keys and values in pages of `PAGE` positions, per layer all key
+  pages [pages, kv_heads, PAGE * head_dim] and then all value pages (keys as
+  [PAGE, head_dim], values transposed as [value_dim, PAGE]), and a table from (slot,
+  position // PAGE) to a page.  A group with a window gives pages back as soon as every
+  position in them has left the window of the sequence's next position; the pages of
+  the first `keep_first` positions are never given back while the sequence lives;
 * a state group holds [layers, slots, *shape], zeroed when a slot is taken.
 
 All decisions are taken on the host; the device only sees the page tables.
@@ -40,10 +41,11 @@ def pages_for(n_tokens: int) -> int:
 class PagedView:
     """What an attention mixer gets for its layer."""
     k_pages: torch.Tensor       # [pages, kv_heads, PAGE, head_dim]
-    v_pages: torch.Tensor       # [pages, kv_heads, head_dim, PAGE]: values lie transposed
+    v_pages: torch.Tensor       # [pages, kv_heads, value_dim, PAGE]: values lie transposed
     page_table: torch.Tensor    # [slots, pages per sequence] int32, on the device
     window: Optional[int]
     group: "PagedGroup"
+    keep_first: int = 0
 
 
 @dataclass
@@ -70,8 +72,12 @@ class PagedGroup:
         if isinstance(request, PagedLatentRequest):
             shape = (len(self.layers), n_pages, PAGE * request.width)
         else:
-            shape = (len(self.layers), 2, n_pages, request.num_kv_heads, PAGE * request.head_dim)
+            self._k_elems = n_pages * request.num_kv_heads * PAGE * request.head_dim
+            shape = (len(self.layers),
+                     self._k_elems + n_pages * request.num_kv_heads * PAGE * request.value_dim)
         self.storage = torch.zeros(shape, dtype=dtype, device=device)
+        # columns of the table that hold the first `keep_first` positions: a window never returns them
+        self.kept_cols = pages_for(getattr(request, "keep_first", 0)) if request.window else 0
         self.table_host = np.full((max_slots, table_width), -1, dtype=np.int32)
         self.table_dev = torch.full((max_slots, table_width), -1, dtype=torch.int32, device=device)
         self.first_live = [0] * max_slots   # first table column that still holds a page
@@ -110,10 +116,12 @@ class PagedGroup:
         keep_from = min(first_needed_key // PAGE, self.n_cols[slot])
         f = self.first_live[slot]
         if keep_from > f:
-            self.pool.give_back(int(p) for p in self.table_host[slot, f:keep_from])
-            self.table_host[slot, f:keep_from] = -1
+            lo = max(f, self.kept_cols)      # columns below hold the kept first positions
+            if keep_from > lo:
+                self.pool.give_back(int(p) for p in self.table_host[slot, lo:keep_from])
+                self.table_host[slot, lo:keep_from] = -1
+                self._dirty.add(slot)
             self.first_live[slot] = keep_from
-            self._dirty.add(slot)
 
     def can_truncate(self, slot: int, new_len: int) -> bool:
         """Whether the keys that position `new_len` will see are still held."""
@@ -130,18 +138,15 @@ class PagedGroup:
         f, c = self.first_live[slot], self.n_cols[slot]
         if keep >= c:
             return
-        lo = max(keep, f)
-        if c > lo:
-            self.pool.give_back(int(p) for p in self.table_host[slot, lo:c])
+        self.pool.give_back(int(p) for p in self.table_host[slot, keep:c] if p >= 0)
         self.table_host[slot, keep:c] = -1
         self.n_cols[slot] = keep
         self.first_live[slot] = min(f, keep)
         self._dirty.add(slot)
 
     def release(self, slot: int) -> None:
-        f, c = self.first_live[slot], self.n_cols[slot]
-        if c > f:
-            self.pool.give_back(int(p) for p in self.table_host[slot, f:c])
+        c = self.n_cols[slot]
+        self.pool.give_back(int(p) for p in self.table_host[slot, :c] if p >= 0)
         self.table_host[slot, :c] = -1
         self.first_live[slot] = 0
         self.n_cols[slot] = 0
@@ -181,9 +186,9 @@ class PagedGroup:
         if isinstance(r, PagedLatentRequest):
             return LatentView(self.storage[i].view(self.n_pages, PAGE, r.width), self.table_dev,
                               r.window, self)
-        k = self.storage[i, 0].view(self.n_pages, r.num_kv_heads, PAGE, r.head_dim)
-        v = self.storage[i, 1].view(self.n_pages, r.num_kv_heads, r.head_dim, PAGE)
-        return PagedView(k, v, self.table_dev, r.window, self)
+        k = self.storage[i, :self._k_elems].view(self.n_pages, r.num_kv_heads, PAGE, r.head_dim)
+        v = self.storage[i, self._k_elems:].view(self.n_pages, r.num_kv_heads, r.value_dim, PAGE)
+        return PagedView(k, v, self.table_dev, r.window, self, r.keep_first if r.window else 0)
 
 
 class StateGroup:
@@ -207,7 +212,7 @@ class Cache:
     (None: nothing, or it reads another entry's cache); "layer" below means such an entry.  `max_tokens` is the most tokens that live sequences hold
     at any time, each sequence's count rounded up to a multiple of PAGE."""
 
-    def __init__(self, requests: Sequence[Union[PagedKVRequest, PagedLatentRequest, StateRequest, None]],
+    def __init__(self, requests: Sequence[Union[PagedKVRequest, PagedLatentRequest, StateRequest, tuple, None]],
                  max_tokens: int, max_slots: Optional[int] = None,
                  max_seq_len: Optional[int] = None, dtype: torch.dtype = torch.bfloat16,
                  device: Union[str, torch.device] = "cuda"):
@@ -223,9 +228,17 @@ class Cache:
         self.paged: List[PagedGroup] = []
         self.states: List[StateGroup] = []
         self._of_layer: Dict[int, Union[PagedGroup, StateGroup]] = {}
-        by_request: Dict[object, List[int]] = {}
+        # A mixer made of several (branches side by side) asks for several things at once: a tuple
+        # of requests, each of which joins the group of its kind under the key (entry, place).
+        self._composite: Dict[int, int] = {}
+        by_request: Dict[object, List[object]] = {}
         for layer, req in enumerate(requests):
-            if req is not None:
+            if isinstance(req, (tuple, list)):
+                self._composite[layer] = len(req)
+                for j, sub in enumerate(req):
+                    if sub is not None:
+                        by_request.setdefault(sub, []).append((layer, j))
+            elif req is not None:
                 by_request.setdefault(req, []).append(layer)
         for req, layers in by_request.items():
             if isinstance(req, (PagedKVRequest, PagedLatentRequest)):
@@ -338,6 +351,9 @@ class Cache:
 
     # ---- views ---------------------------------------------------------------------
     def view(self, layer: int):
+        if layer in self._composite:
+            keys = [(layer, j) for j in range(self._composite[layer])]
+            return tuple(None if k not in self._of_layer else self._of_layer[k].view(k) for k in keys)
         g = self._of_layer.get(layer)
         return None if g is None else g.view(layer)
 

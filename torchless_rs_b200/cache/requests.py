@@ -11,10 +11,18 @@ import torch
 @dataclass(frozen=True)
 class PagedKVRequest:
     """Keys and values of every position (window None), or of the last `window`
-    positions only."""
+    positions only; with `keep_first`, the sequence's first `keep_first` positions stay
+    visible (and held) whatever the window.  `v_head_dim`: the size of a value where it is
+    not the size of a key."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    keep_first: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim if self.v_head_dim else self.head_dim
 
 
 @dataclass(frozen=True)

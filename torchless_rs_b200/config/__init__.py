@@ -3,11 +3,12 @@ from .reader import KeyReader, read_config_json
 from .spec import LayerSpec, ModelSpec, PartSpec
 from .mistral import MistralConfig
 from .kikopel import KikopelConfig
+from .tovapel import TovapelConfig
 from .registry import (architecture_names, config_from_dict, load_config,
                        register_architecture)
 
 __all__ = [
     "ConfigError", "UnknownArchitectureError", "KeyReader", "read_config_json",
-    "LayerSpec", "ModelSpec", "PartSpec", "MistralConfig", "KikopelConfig", "architecture_names",
+    "LayerSpec", "ModelSpec", "PartSpec", "MistralConfig", "KikopelConfig", "TovapelConfig", "architecture_names",
     "config_from_dict", "load_config", "register_architecture",
 ]

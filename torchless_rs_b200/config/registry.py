@@ -61,6 +61,8 @@ def _register_builtin() -> None:
     register_architecture("MistralForCausalLM", "mistral", "mistralai")(MistralConfig)
     from .kikopel import KikopelConfig
     register_architecture("Kikopel")(KikopelConfig)
+    from .tovapel import TovapelConfig
+    register_architecture("Tovapel")(TovapelConfig)
 
 
 _register_builtin()

@@ -75,6 +75,9 @@ class ModelSpec:
     logit_softcap: Optional[float] = None        # logits <- cap * tanh(logits / cap)
     embedding_addend: Optional[PartSpec] = None  # a registered part that adds to the embedded tokens
                                                  #   (it may keep per-sequence state)
+    streams: Optional[int] = None                # residual streams kept side by side: every one starts as
+                                                 #   the embedded token, the layers' blocks read and write
+                                                 #   all of them, their sum goes to the final norm
 
     def validate(self) -> None:
         from .errors import ConfigError
@@ -85,6 +88,8 @@ class ModelSpec:
             raise ConfigError("a position table needs max_positions > 0")
         if self.logit_softcap is not None and not self.logit_softcap > 0:
             raise ConfigError("logit_softcap must be positive")
+        if self.streams is not None and not 1 <= self.streams <= 8:
+            raise ConfigError("streams must lie between 1 and 8")
         for i, layer in enumerate(self.layers):
             for role in ("mixer", "feed_forward", *layer.norms):
                 if role not in layer.names:

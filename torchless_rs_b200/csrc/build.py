@@ -32,7 +32,8 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
               f"-DTL_PAGE={PAGE_TOKENS}"]
 
 _CORE_SOURCES = ("elementwise.cu", "gemm_generic.cu", "attention_generic.cu", "branch_elementwise.cu",
-                 "latent_attention.cu", "linear_recurrence.cu")
+                 "latent_attention.cu", "linear_recurrence.cu", "hyper_elementwise.cu", "sink_attention.cu",
+                 "gla_recurrence.cu", "moe.cu")
 
 # library name -> (sources, defines)
 LIBRARIES: Dict[str, Tuple[Sequence[str], Sequence[str]]] = {

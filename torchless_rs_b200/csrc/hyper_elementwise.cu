@@ -1,0 +1,237 @@
+// Residual streams kept several at a time (hyper-connections), and the small row kernels of
+// mixers that run branches side by side.  Everything here is bound by memory; sums, norms and
+// the streams themselves are 32-bit, `act_t` is what feeds the matrix products.
+//
+// Streams lie token-major: xs[t, s, :] for s < S, so one token's streams are one contiguous run.
+// A sublayer reads   u = sum_s a[s] xs[t, s, :]   through a norm, and its output y goes back as
+//   xs'[t, j, :] = sum_s M[s, j] xs[t, s, :] + b[j] y[t, :]          (M is indexed [from, to])
+// The kernel that writes a sublayer's output can also do the next sublayer's read and norm, so
+// the streams cross the memory once per sublayer.
+#include "common.cuh"
+
+#define HC_MAX_STREAMS 8
+
+// xs[t, s, :] = x[t, :] for every s.
+__global__ void stream_spread_kernel(const float* __restrict__ x, float* __restrict__ xs, int H, int S) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const float* src = x + (size_t)t * H;
+  float* dst = xs + (size_t)t * S * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = src[i];
+    for (int s = 0; s < S; ++s) dst[(size_t)s * H + i] = v;
+  }
+}
+
+extern "C" int TL_NAME(tl_stream_spread)(const float* x, float* xs, int T, int H, int S, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (S < 1 || H < 1) return TL_ERR_BAD_ARG;
+  return tl_launch(stream_spread_kernel, dim3(T), dim3(256), 0, stream, x, xs, H, S);
+}
+
+// x[r, :] = sum_s xs[rows[r], s, :]   (rows null: row r itself), streams added in their order.
+__global__ void stream_sum_kernel(const float* __restrict__ xs, const int* __restrict__ rows,
+                                  float* __restrict__ x, int H, int S) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const int t = rows != nullptr ? rows[r] : r;
+  const float* src = xs + (size_t)t * S * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float a = src[i];
+    for (int s = 1; s < S; ++s) a += src[(size_t)s * H + i];
+    x[(size_t)r * H + i] = a;
+  }
+}
+
+extern "C" int TL_NAME(tl_stream_sum)(const float* xs, const int* rows, float* x, int R, int H, int S,
+                                      cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (S < 1 || H < 1) return TL_ERR_BAD_ARG;
+  return tl_launch(stream_sum_kernel, dim3(R), dim3(256), 0, stream, xs, rows, x, H, S);
+}
+
+// out[t, :] = act( u / sqrt(mean(u^2) + eps) * w ),  u = sum_s a[s] xs[t, s, :].
+// `w` is the 32-bit factor per coordinate (a norm whose stored weight lies around zero hands in
+// 1 + weight).  u is kept in shared memory between the two passes (H floats).
+__global__ void __launch_bounds__(256)
+hc_read_norm_kernel(const float* __restrict__ xs, const float* __restrict__ a, const float* __restrict__ w,
+                    float eps, act_t* __restrict__ out, int H, int S) {
+  extern __shared__ float u_s[];
+  __shared__ float scratch[33];
+  __shared__ float a_s[HC_MAX_STREAMS];
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x < S) a_s[threadIdx.x] = a[threadIdx.x];
+  __syncthreads();
+  const int t = blockIdx.x;
+  const float* src = xs + (size_t)t * S * H;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float u = a_s[0] * src[i];
+    for (int s = 1; s < S; ++s) u = fmaf(a_s[s], src[(size_t)s * H + i], u);
+    u_s[i] = u;
+    ss = fmaf(u, u, ss);
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[(size_t)t * H + i] = from_f32<act_t>(u_s[i] * inv * w[i]);
+}
+
+extern "C" int TL_NAME(tl_hc_read_norm)(const float* xs, const float* a, const float* w, float eps, void* out,
+                                        int T, int H, int S, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (S < 1 || S > HC_MAX_STREAMS || H < 1) return TL_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return TL_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(hc_read_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return tl_launch(hc_read_norm_kernel, dim3(T), dim3(256), smem, stream, xs, a, w, eps, (act_t*)out, H, S);
+}
+
+// xs'[t, j, :] = sum_s M[s, j] xs[t, s, :] + b[j] y[t, :], in place (a coordinate's S values are
+// read before any is written).  With `a2` given the kernel goes on to the next sublayer's read:
+// out2[t, :] = act( u2 / rms(u2) * w2 ) with u2 = sum_j a2[j] xs'[t, j, :].
+__global__ void __launch_bounds__(256)
+hc_write_kernel(float* __restrict__ xs, const float* __restrict__ M, const float* __restrict__ b,
+                const float* __restrict__ y, int ldy, int H, int S, const float* __restrict__ a2,
+                const float* __restrict__ w2, float eps2, act_t* __restrict__ out2) {
+  extern __shared__ float u_s[];
+  __shared__ float scratch[33];
+  __shared__ float m_s[HC_MAX_STREAMS * HC_MAX_STREAMS], b_s[HC_MAX_STREAMS], a_s[HC_MAX_STREAMS];
+  pdl_wait();
+  pdl_launch_dependents();
+  if (threadIdx.x < S * S) m_s[threadIdx.x] = M[threadIdx.x];
+  if (threadIdx.x < S) {
+    b_s[threadIdx.x] = b[threadIdx.x];
+    a_s[threadIdx.x] = a2 != nullptr ? a2[threadIdx.x] : 0.0f;
+  }
+  __syncthreads();
+  const int t = blockIdx.x;
+  float* row = xs + (size_t)t * S * H;
+  const float* yr = y + (size_t)t * ldy;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float old[HC_MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < HC_MAX_STREAMS; ++s) old[s] = s < S ? row[(size_t)s * H + i] : 0.0f;
+    const float yv = yr[i];
+    float u = 0.0f;
+#pragma unroll
+    for (int j = 0; j < HC_MAX_STREAMS; ++j) {
+      if (j < S) {
+        float v = m_s[j] * old[0];
+#pragma unroll
+        for (int s = 1; s < HC_MAX_STREAMS; ++s)
+          if (s < S) v = fmaf(m_s[s * S + j], old[s], v);
+        v = fmaf(b_s[j], yv, v);
+        row[(size_t)j * H + i] = v;
+        u = j == 0 ? a_s[0] * v : fmaf(a_s[j], v, u);
+      }
+    }
+    if (a2 != nullptr) {
+      u_s[i] = u;
+      ss = fmaf(u, u, ss);
+    }
+  }
+  if (a2 == nullptr) return;
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps2);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out2[(size_t)t * H + i] = from_f32<act_t>(u_s[i] * inv * w2[i]);
+}
+
+extern "C" int TL_NAME(tl_hc_write)(float* xs, const float* M, const float* b, const float* y, int ldy, int T,
+                                    int H, int S, const float* a2, const float* w2, float eps2, void* out2,
+                                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (S < 1 || S > HC_MAX_STREAMS || H < 1) return TL_ERR_UNSUPPORTED;
+  if (a2 != nullptr && (w2 == nullptr || out2 == nullptr)) return TL_ERR_BAD_ARG;
+  const size_t smem = a2 != nullptr ? (size_t)H * sizeof(float) : 0;
+  if (smem > 200 * 1024) return TL_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(hc_write_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  return tl_launch(hc_write_kernel, dim3(T), dim3(256), smem, stream, xs, M, b, y, ldy, H, S, a2, w2, eps2,
+                   (act_t*)out2);
+}
+
+// Branches side by side: out[t, :] (+)= (1 / n) sum_b y_b[t, :] / sqrt(mean(y_b[t]^2) + eps) * w_b[:],
+// each branch's output normalised over the whole row with its own 32-bit weight.
+#define BR_MAX 4
+struct BranchPtrs {
+  const float* y[BR_MAX];
+  const float* w[BR_MAX];
+};
+
+__global__ void __launch_bounds__(256)
+branch_norm_mean_kernel(BranchPtrs p, int n, int H, float eps, float* __restrict__ out, int accumulate) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  float inv[BR_MAX];
+  for (int b = 0; b < n; ++b) {
+    const float* y = p.y[b] + (size_t)t * H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) ss = fmaf(y[i], y[i], ss);
+    const float total = block_sum(ss, scratch);
+    inv[b] = 1.0f / sqrtf(total / (float)H + eps);
+  }
+  const float share = 1.0f / (float)n;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float a = 0.0f;
+    for (int b = 0; b < n; ++b) a += p.y[b][(size_t)t * H + i] * inv[b] * p.w[b][i];
+    a *= share;
+    float* o = out + (size_t)t * H + i;
+    *o = accumulate ? *o + a : a;
+  }
+}
+
+extern "C" int TL_NAME(tl_branch_norm_mean)(const float* const* ys, const float* const* ws, int n, int T, int H,
+                                            float eps, float* out, int accumulate, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n < 1 || n > BR_MAX) return TL_ERR_UNSUPPORTED;
+  BranchPtrs p = {};
+  for (int b = 0; b < n; ++b) {
+    p.y[b] = ys[b];
+    p.w[b] = ws[b];
+  }
+  return tl_launch(branch_norm_mean_kernel, dim3(T), dim3(256), 0, stream, p, n, H, eps, out, accumulate);
+}
+
+// Per-head output norm with a gate: out[t, h, :] = act( o[t, h, :] / rms * w[:] * silu(g[t, h, :]) ),
+// the norm over the head's `vdim` entries with one weight vector for all heads.  A warp per (t, h).
+__global__ void __launch_bounds__(256)
+headnorm_silu_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
+                          const float* __restrict__ g, int ldg, act_t* __restrict__ out, int rows, int heads,
+                          int vdim) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int t = r / heads, h = r - t * heads;
+  const float* src = o + (size_t)r * vdim;
+  const float* gate = g + (size_t)t * ldg + (size_t)h * vdim;
+  float ss = 0.0f;
+  for (int i = lane; i < vdim; i += 32) ss = fmaf(src[i], src[i], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+  for (int i = lane; i < vdim; i += 32) {
+    const float z = gate[i];
+    out[(size_t)r * vdim + i] = from_f32<act_t>(src[i] * inv * w[i] * (z / (1.0f + expf(-z))));
+  }
+}
+
+extern "C" int TL_NAME(tl_headnorm_silu_gate)(const float* o, const float* w, float eps, const float* g, int ldg,
+                                              void* out, int T, int heads, int vdim, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (heads < 1 || vdim < 1) return TL_ERR_BAD_ARG;
+  const long long rows = (long long)T * heads;
+  if (rows > 0x7fffffffLL) return TL_ERR_UNSUPPORTED;
+  const unsigned blocks = (unsigned)((rows + 7) / 8);
+  return tl_launch(headnorm_silu_gate_kernel, dim3(blocks), dim3(256), 0, stream, o, w, eps, g, ldg, (act_t*)out,
+                   (int)rows, heads, vdim);
+}

@@ -1,0 +1,289 @@
+// Mixture of experts: router, the grouping of (token, expert) pairs by expert, the experts'
+// products over each group, and the weighted sum per token.
+//
+//   scores s = softmax(z) over all router outputs (32-bit); the choice is made on s + correction,
+//   the `top` largest (ties: the lower index); the weights are the chosen s, not renormalised.
+//   Router outputs from `experts` on have no matrices: such an expert hands its input through.
+//   A real expert: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit),
+//                  y = W_down( g * sigmoid(alpha g) * (u + 1) ).
+//
+// Nothing here needs the host: counts and offsets stay on the device, and the product kernels are
+// launched over an upper bound of tiles, of which a block finds its own (expert, rows) or leaves.
+// A token's result is the sum of its chosen experts' outputs in the order of its choice, so it does
+// not depend on what else is in the step.
+#include "common.cuh"
+
+#define MOE_MAX_PER_LANE 16     // router outputs per lane: up to 512 experts
+
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ corr, int n_out, int top,
+                 int* __restrict__ idx, float* __restrict__ wt, int T) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const float* row = z + (size_t)t * ldz;
+  float s[MOE_MAX_PER_LANE], c[MOE_MAX_PER_LANE];
+  float m = -INFINITY;
+#pragma unroll
+  for (int r = 0; r < MOE_MAX_PER_LANE; ++r) {
+    const int e = lane + 32 * r;
+    s[r] = e < n_out ? row[e] : -INFINITY;
+    m = fmaxf(m, s[r]);
+  }
+  m = warp_max(m);
+  float sum = 0.0f;
+#pragma unroll
+  for (int r = 0; r < MOE_MAX_PER_LANE; ++r) {
+    s[r] = lane + 32 * r < n_out ? expf(s[r] - m) : 0.0f;
+    sum += s[r];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int r = 0; r < MOE_MAX_PER_LANE; ++r) {
+    const int e = lane + 32 * r;
+    s[r] = s[r] / sum;
+    c[r] = e < n_out ? s[r] + (corr != nullptr ? corr[e] : 0.0f) : -INFINITY;
+  }
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY, best_s = 0.0f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int r = 0; r < MOE_MAX_PER_LANE; ++r) {
+      const int e = lane + 32 * r;
+      if (e < n_out && c[r] > best) {    // r rises with e, so a tie keeps the lower index
+        best = c[r];
+        best_e = e;
+        best_s = s[r];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+        best_s = os;
+      }
+    }
+    if (lane == 0) {
+      idx[(size_t)t * top + k] = best_e;
+      wt[(size_t)t * top + k] = best_s;
+    }
+#pragma unroll
+    for (int r = 0; r < MOE_MAX_PER_LANE; ++r)
+      if (lane + 32 * r == best_e) c[r] = -INFINITY;
+  }
+}
+
+extern "C" int TL_NAME(tl_moe_route)(const float* z, int ldz, const float* corr, int n_out, int top, int* idx,
+                                     float* wt, int T, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (n_out < 1 || top < 1 || top > n_out) return TL_ERR_BAD_ARG;
+  if (n_out > 32 * MOE_MAX_PER_LANE) return TL_ERR_UNSUPPORTED;
+  return tl_launch(moe_route_kernel, dim3((T + 7) / 8), dim3(256), 0, stream, z, ldz, corr, n_out, top, idx, wt,
+                   T);
+}
+
+// Groups the pairs by expert.  offsets[e] .. offsets[e + 1] are the rows of expert e < E in the
+// grouped order; row_token[row] is the token a row belongs to; row_of[pair] is the row of pair
+// (t, k), or -1 for a pair whose expert hands its input through.  One block: the pairs of a step
+// are few against what the products move.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ idx, int n_pairs, int top, int E, int* __restrict__ offsets,
+                int* __restrict__ row_token, int* __restrict__ row_of) {
+  extern __shared__ int sm[];
+  int* count = sm;            // [E]
+  int* start = sm + E;        // [E + 1]
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = idx[p];
+    if (e < E) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = at;
+      at += count[e];
+    }
+    start[E] = at;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    offsets[e] = start[e];
+    if (e < E) count[e] = 0;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = idx[p];
+    if (e < E) {
+      const int row = start[e] + atomicAdd(&count[e], 1);
+      row_token[row] = p / top;
+      row_of[p] = row;
+    } else {
+      row_of[p] = -1;
+    }
+  }
+}
+
+extern "C" int TL_NAME(tl_moe_plan)(const int* idx, int n_pairs, int top, int E, int* offsets, int* row_token,
+                                    int* row_of, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (E < 0 || E > 4096 || top < 1) return TL_ERR_UNSUPPORTED;
+  return tl_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, idx, n_pairs,
+                   top, E, offsets, row_token, row_of);
+}
+
+// ---------------------------------------------------------------------------
+// The experts' products over the grouped rows, on CUDA cores with 32-bit accumulation:
+//   UP:    C[row, n] (act_t) = act( A[row_token[row]] . Wg_e[n], A[row_token[row]] . Wu_e[n] )
+//          with W_e = [2 N, K]: N gate rows, then N up rows
+//   DOWN:  C[row, n] (float) = A[row] . W_e[n],  W_e = [N, K]
+// Block y walks an upper bound of row tiles (pairs / 64 + experts); it finds the expert whose
+// rows its tile covers from the offsets, or leaves.
+// ---------------------------------------------------------------------------
+#define GBM 64
+#define GBN 64
+#define GBK 16
+
+template <bool UP>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const act_t* __restrict__ A, int lda, const int* __restrict__ row_token,
+                const act_t* __restrict__ W, void* __restrict__ C, int ldc, const int* __restrict__ offsets,
+                int E, int N, int K, float limit, float alpha) {
+  __shared__ float As[GBK][GBM + 4];
+  __shared__ float Ws[GBK][GBN + 4];
+  __shared__ float Us[UP ? GBK : 1][GBN + 4];
+  __shared__ int src_row[GBM];
+  __shared__ int tile_info[3];   // expert, first row, rows
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    int tile = blockIdx.y, e = 0, found = -1;
+    for (; e < E; ++e) {
+      const int cnt = offsets[e + 1] - offsets[e];
+      const int tiles = (cnt + GBM - 1) / GBM;
+      if (tile < tiles) {
+        found = e;
+        break;
+      }
+      tile -= tiles;
+    }
+    tile_info[0] = found;
+    if (found >= 0) {
+      tile_info[1] = offsets[found] + tile * GBM;
+      const int left = offsets[found + 1] - tile_info[1];
+      tile_info[2] = left < GBM ? left : GBM;
+    }
+  }
+  __syncthreads();
+  const int e = tile_info[0];
+  if (e < 0) return;
+  const int r0 = tile_info[1], rows = tile_info[2];
+  if (tid < GBM) src_row[tid] = tid < rows ? (UP ? row_token[r0 + tid] : r0 + tid) : -1;
+  __syncthreads();
+  const act_t* We = W + (size_t)e * (UP ? 2 : 1) * N * K;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int n0 = blockIdx.x * GBN;
+  float acc[4][4] = {}, acu[4][4] = {};
+  const int lrow = tid >> 2, lk = (tid & 3) * 4;
+  const int arow = src_row[lrow];
+  for (int k0 = 0; k0 < K; k0 += GBK) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = k0 + lk + j;
+      const int wn = n0 + lrow;
+      As[lk + j][lrow] = (arow >= 0 && k < K) ? to_f32(A[(size_t)arow * lda + k]) : 0.0f;
+      Ws[lk + j][lrow] = (wn < N && k < K) ? to_f32(We[(size_t)wn * K + k]) : 0.0f;
+      if (UP) Us[lk + j][lrow] = (wn < N && k < K) ? to_f32(We[(size_t)(N + wn) * K + k]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GBK; ++k) {
+      float a[4], w[4], u[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = Ws[k][tx * 4 + j];
+      if (UP) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) u[j] = Us[k][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+          if (UP) acu[i][j] = fmaf(a[i], u[j], acu[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = ty * 4 + i;
+    if (m >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      if (UP) {
+        const float g = fminf(acc[i][j], limit);
+        const float u = fminf(fmaxf(acu[i][j], -limit), limit);
+        ((act_t*)C)[(size_t)(r0 + m) * ldc + n] = from_f32<act_t>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+      } else {
+        ((float*)C)[(size_t)(r0 + m) * ldc + n] = acc[i][j];
+      }
+    }
+  }
+}
+
+extern "C" int TL_NAME(tl_moe_gemm)(const void* A, int lda, const int* row_token, const void* W, void* C, int ldc,
+                                    const int* offsets, int E, int max_rows, int N, int K, int up, float limit,
+                                    float alpha, cudaStream_t stream) {
+  if (max_rows <= 0 || E <= 0) return 0;
+  if (N < 1 || K < 1) return TL_ERR_BAD_ARG;
+  const int tiles = (max_rows + GBM - 1) / GBM + E;
+  if (tiles > 65535) return TL_ERR_UNSUPPORTED;
+  dim3 grid((N + GBN - 1) / GBN, tiles);
+  if (up)
+    return tl_launch(moe_gemm_kernel<true>, grid, dim3(256), 0, stream, (const act_t*)A, lda, row_token,
+                     (const act_t*)W, C, ldc, offsets, E, N, K, limit, alpha);
+  return tl_launch(moe_gemm_kernel<false>, grid, dim3(256), 0, stream, (const act_t*)A, lda, row_token,
+                   (const act_t*)W, C, ldc, offsets, E, N, K, limit, alpha);
+}
+
+// out[t, :] (+)= sum_k wt[t, k] * ( row_of[t, k] >= 0 ? yk[row_of[t, k], :] : h[t, :] ), k in order.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ yk, const int* __restrict__ row_of, const float* __restrict__ wt,
+                   const act_t* __restrict__ h, float* __restrict__ out, int ldo, int H, int top, int accumulate) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float a = 0.0f;
+    for (int k = 0; k < top; ++k) {
+      const int row = row_of[(size_t)t * top + k];
+      const float v = row >= 0 ? yk[(size_t)row * H + i] : to_f32(h[(size_t)t * H + i]);
+      a = fmaf(wt[(size_t)t * top + k], v, a);
+    }
+    float* o = out + (size_t)t * ldo + i;
+    *o = accumulate ? *o + a : a;
+  }
+}
+
+extern "C" int TL_NAME(tl_moe_combine)(const float* yk, const int* row_of, const float* wt, const void* h,
+                                       float* out, int ldo, int T, int H, int top, int accumulate,
+                                       cudaStream_t stream) {
+  if (T <= 0) return 0;
+  return tl_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, yk, row_of, wt, (const act_t*)h, out, ldo,
+                   H, top, accumulate);
+}

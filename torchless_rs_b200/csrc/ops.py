@@ -133,7 +133,10 @@ class CoreOps:
         self.lib = build.load_library(f"core_{self.suffix}")
         for base in ("tl_embed", "tl_softcap", "tl_advance_step", "tl_regroup_step", "tl_convert", "tl_rmsnorm", "tl_rope_cache_write", "tl_silu_mul",
                      "tl_gemm_generic", "tl_attn_generic", "tl_pair_embed_add", "tl_branch_norm_add", "tl_poly_norm",
-                     "tl_latent_prep", "tl_headwise_gemm", "tl_latent_attn", "tl_gated_scan", "tl_gated_scan_groups"):
+                     "tl_latent_prep", "tl_headwise_gemm", "tl_latent_attn", "tl_gated_scan", "tl_gated_scan_groups",
+                     "tl_stream_spread", "tl_stream_sum", "tl_hc_read_norm", "tl_hc_write", "tl_branch_norm_mean",
+                     "tl_headnorm_silu_gate", "tl_qk_norm_cache_write", "tl_sink_attn", "tl_gla_scan",
+                     "tl_moe_route", "tl_moe_plan", "tl_moe_gemm", "tl_moe_combine"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
             setattr(self, "_" + base, fn)
@@ -492,6 +495,238 @@ class CoreOps:
             _check(0, "scan_gates")
         if groups > 1:
             _check(0, "scan_sum_slices")
+
+    # ---- several residual streams (hyper-connections) ---------------------------------------------
+    def stream_spread(self, x: torch.Tensor, xs: torch.Tensor) -> None:
+        """xs[t, s, :] = x[t, :] for every stream s."""
+        _need(x, torch.float32, "stream")
+        _need(xs, torch.float32, "streams")
+        T, S, H = xs.shape
+        if x.shape != (T, H):
+            raise KernelError("stream_spread: sizes do not match")
+        _check(self._tl_stream_spread(_ptr(x), _ptr(xs), c_int(T), c_int(H), c_int(S), _stream()), "stream_spread")
+
+    def stream_sum(self, xs: torch.Tensor, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        """x[r, :] = sum_s xs[rows[r], s, :] (all rows in order without `rows`)."""
+        _need(x, torch.float32, "stream")
+        _need(xs, torch.float32, "streams")
+        _, S, H = xs.shape
+        if x.shape[1] != H:
+            raise KernelError("stream_sum: sizes do not match")
+        if rows is not None:
+            _need(rows, torch.int32, "stream_sum rows")
+        _check(self._tl_stream_sum(_ptr(xs), _ptr(rows), _ptr(x), c_int(x.shape[0]), c_int(H), c_int(S), _stream()),
+               "stream_sum")
+
+    def hc_read_norm(self, xs: torch.Tensor, a: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+        """out[t] = act(u / rms(u) * w) with u = sum_s a[s] xs[t, s]; `w` 32-bit per coordinate."""
+        _need(xs, torch.float32, "streams")
+        _need(a, torch.float32, "stream read weights")
+        _need(w, torch.float32, "norm factor")
+        _need(out, self.act_dtype, "normed input")
+        T, S, H = xs.shape
+        if a.numel() != S or w.numel() != H or out.shape != (T, H):
+            raise KernelError("hc_read_norm: sizes do not match")
+        _check(self._tl_hc_read_norm(_ptr(xs), _ptr(a), _ptr(w), c_float(eps), _ptr(out), c_int(T), c_int(H),
+                                     c_int(S), _stream()), "hc_read_norm")
+
+    def hc_write(self, xs: torch.Tensor, mix: torch.Tensor, b: torch.Tensor, y: torch.Tensor,
+                 next_read=None) -> None:
+        """xs'[t, j] = sum_s mix[s, j] xs[t, s] + b[j] y[t], in place.  `next_read` = (a, w, eps, out): the
+        kernel also does the next sublayer's read and norm (see `hc_read_norm`) on the new streams."""
+        _need(xs, torch.float32, "streams")
+        _need(mix, torch.float32, "stream mix")
+        _need(b, torch.float32, "stream write weights")
+        _need(y, torch.float32, "sublayer output", contiguous=False)
+        T, S, H = xs.shape
+        if mix.shape != (S, S) or b.numel() != S or y.shape != (T, H) or y.stride(1) != 1:
+            raise KernelError("hc_write: sizes do not match")
+        a2 = w2 = out2 = None
+        eps2 = 0.0
+        if next_read is not None:
+            a2, w2, eps2, out2 = next_read
+            _need(a2, torch.float32, "stream read weights")
+            _need(w2, torch.float32, "norm factor")
+            _need(out2, self.act_dtype, "normed input")
+            if a2.numel() != S or w2.numel() != H or out2.shape != (T, H):
+                raise KernelError("hc_write: sizes of the next read do not match")
+        _check(self._tl_hc_write(_ptr(xs), _ptr(mix), _ptr(b), _ptr(y), c_int(y.stride(0)), c_int(T), c_int(H),
+                                 c_int(S), _ptr(a2), _ptr(w2), c_float(eps2), _ptr(out2), _stream()), "hc_write")
+
+    def branch_norm_mean(self, ys, ws, eps: float, out: torch.Tensor, accumulate: bool) -> None:
+        """out (+)= mean over the branches of y_b / rms(y_b) * w_b, row by row (up to 4 branches)."""
+        _need(out, torch.float32, "mixer output")
+        T, H = out.shape
+        for y, w in zip(ys, ws):
+            _need(y, torch.float32, "branch output")
+            _need(w, torch.float32, "branch norm weight")
+            if y.shape != (T, H) or w.numel() != H:
+                raise KernelError("branch_norm_mean: sizes do not match")
+        n = len(ys)
+        yp = (c_void_p * n)(*[y.data_ptr() for y in ys])
+        wp = (c_void_p * n)(*[w.data_ptr() for w in ws])
+        _check(self._tl_branch_norm_mean(yp, wp, c_int(n), c_int(T), c_int(H), c_float(eps), _ptr(out),
+                                         c_int(1 if accumulate else 0), _stream()), "branch_norm_mean")
+
+    def headnorm_silu_gate(self, o: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tensor,
+                           out: torch.Tensor, heads: int, vdim: int) -> None:
+        """out[t, h] = act(o[t, h] / rms(o[t, h]) * w * silu(gate[t, h])), the norm over a head's entries."""
+        _need(o, torch.float32, "head outputs")
+        _need(w, torch.float32, "head norm weight")
+        _need(gate, torch.float32, "gate", contiguous=False)
+        _need(out, self.act_dtype, "gated output")
+        T = o.shape[0]
+        if o.shape != (T, heads * vdim) or out.shape != o.shape or gate.shape != o.shape or gate.stride(1) != 1 or \
+                w.numel() != vdim:
+            raise KernelError("headnorm_silu_gate: sizes do not match")
+        _check(self._tl_headnorm_silu_gate(_ptr(o), _ptr(w), c_float(eps), _ptr(gate), c_int(gate.stride(0)),
+                                           _ptr(out), c_int(T), c_int(heads), c_int(vdim), _stream()),
+               "headnorm_silu_gate")
+
+    # ---- attention with a sink, capped scores and a window that keeps the first keys --------------
+    def qk_norm_cache_write(self, z: torch.Tensor, bias: Optional[torch.Tensor], qw: Optional[torch.Tensor],
+                            kw: Optional[torch.Tensor], eps: float, q_out: torch.Tensor, k_pages: torch.Tensor,
+                            v_pages: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+                            seq_slot: torch.Tensor, page_table: torch.Tensor, nh: int, nkv: int, dim: int,
+                            vdim: int) -> None:
+        """The projections `z` (32-bit rows: q heads, k heads, v heads) get `bias`; q and k are RMS-normed per
+        head with the weights `qw` / `kw` (None: no norm); q goes to `q_out`, k and v into the pages."""
+        _need(z, torch.float32, "projections", contiguous=False)
+        _need(q_out, self.act_dtype, "q out")
+        _need(k_pages, self.act_dtype, "k pages")
+        _need(v_pages, self.act_dtype, "v pages")
+        _need(page_table, torch.int32, "page table")
+        T = z.shape[0]
+        cols = (nh + nkv) * dim + nkv * vdim
+        if z.shape[1] < cols or z.stride(1) != 1 or q_out.shape != (T, nh * dim) or \
+                k_pages.shape[1:] != (nkv, PAGE, dim) or v_pages.shape[1:] != (nkv, vdim, PAGE):
+            raise KernelError("qk_norm_cache_write: sizes do not match")
+        for t, n, what in ((bias, cols, "bias"), (qw, dim, "q norm weight"), (kw, dim, "k norm weight")):
+            if t is not None:
+                _need(t, torch.float32, what)
+                if t.numel() != n:
+                    raise KernelError(f"qk_norm_cache_write: {what} must have {n} entries")
+        _check(self._tl_qk_norm_cache_write(
+            _ptr(z), c_int(z.stride(0)), _ptr(bias), _ptr(qw), _ptr(kw), c_float(eps), _ptr(q_out), _ptr(k_pages),
+            _ptr(v_pages), _ptr(token_pos), _ptr(token_seq), _ptr(seq_slot), _ptr(page_table),
+            c_int(page_table.stride(0)), c_int(T), c_int(nh), c_int(nkv), c_int(dim), c_int(vdim), _stream()),
+            "qk_norm_cache_write")
+
+    def sink_attn(self, q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, gate: Optional[torch.Tensor],
+                  sink: Optional[torch.Tensor], out: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+                  seq_slot: torch.Tensor, page_table: torch.Tensor, nh: int, nkv: int, dim: int, vdim: int,
+                  window: Optional[int], keep_first: int, scale: float, softcap: Optional[float]) -> None:
+        """out[t, h] = sigmoid(gate[t, h]) * sum_j p_j v_j over the visible keys j (j <= i and (i - j < window
+        or j < keep_first)), scores capped by `softcap`, the softmax's denominator also holding exp(sink[h])."""
+        for t, n in ((q, "attn q"), (k_pages, "k pages"), (v_pages, "v pages"), (out, "attn out")):
+            _need(t, self.act_dtype, n)
+        _need(page_table, torch.int32, "page table")
+        T = q.shape[0]
+        if q.shape != (T, nh * dim) or out.shape != (T, nh * vdim) or k_pages.shape[1:] != (nkv, PAGE, dim) or \
+                v_pages.shape[1:] != (nkv, vdim, PAGE):
+            raise KernelError("sink_attn: sizes do not match")
+        ldg = 0
+        if gate is not None:
+            _need(gate, torch.float32, "head gate", contiguous=False)
+            if gate.shape != (T, nh) or gate.stride(1) != 1:
+                raise KernelError("sink_attn: the gate must be [tokens, heads]")
+            ldg = gate.stride(0)
+        if sink is not None:
+            _need(sink, torch.float32, "sink")
+            if sink.numel() != nh:
+                raise KernelError("sink_attn: one sink per head is needed")
+        _check(self._tl_sink_attn(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(gate), c_int(ldg), _ptr(sink), _ptr(out), _ptr(token_pos),
+            _ptr(token_seq), _ptr(seq_slot), _ptr(page_table), c_int(page_table.stride(0)), c_int(T), c_int(nh),
+            c_int(nkv), c_int(dim), c_int(vdim), c_int(window or 0), c_int(keep_first or 0), c_float(scale),
+            c_float(softcap or 0.0), _stream()), "sink_attn")
+
+    # ---- gated linear attention ---------------------------------------------------------------------
+    def gla_scan(self, zq: torch.Tensor, zk: torch.Tensor, zv: torch.Tensor, za: torch.Tensor,
+                 bias: Optional[torch.Tensor], tau: float, q_scale: float, state: torch.Tensor, out: torch.Tensor,
+                 seq_start: torch.Tensor, seq_slot: torch.Tensor, heads: int, dim: int, vdim: int) -> None:
+        """S <- diag(alpha) S + k v^T, o = S^T (q * q_scale) over each sequence's tokens of the step, from and
+        into `state` [slots, heads, dim, vdim]; alpha = sigmoid(za + bias)^(1 / tau).  zq, zk, zv are column
+        ranges of one 32-bit product (one row stride); `za` may be overwritten with the decays."""
+        for t, n in ((zq, "q"), (zk, "k"), (zv, "v"), (za, "decay pre-activations")):
+            _need(t, torch.float32, "recurrence " + n, contiguous=False)
+            if t.stride(1) != 1:
+                raise KernelError("gla_scan: rows must be contiguous")
+        _need(state, torch.float32, "recurrent state")
+        _need(out, torch.float32, "recurrence out")
+        T = zq.shape[0]
+        if not (zq.stride(0) == zk.stride(0) == zv.stride(0)) or zq.shape[1] != heads * dim or \
+                zk.shape[1] != heads * dim or zv.shape[1] != heads * vdim or za.shape != (T, heads * dim) or \
+                out.shape != (T, heads * vdim) or state.shape[1:] != (heads, dim, vdim):
+            raise KernelError("gla_scan: sizes do not match")
+        if bias is not None:
+            _need(bias, torch.float32, "decay bias")
+        _check(self._tl_gla_scan(_ptr(zq), _ptr(zk), _ptr(zv), c_int(zq.stride(0)), _ptr(za), c_int(za.stride(0)),
+                                 _ptr(bias), c_float(tau), c_float(q_scale), _ptr(state), _ptr(out),
+                                 c_int(out.stride(0)), _ptr(seq_start), _ptr(seq_slot), c_int(T),
+                                 c_int(seq_slot.numel()), c_int(heads), c_int(dim), c_int(vdim), _stream()),
+               "gla_scan")
+        if T > 4 * seq_slot.numel():
+            _check(0, "gla_decay")
+
+    # ---- mixture of experts ---------------------------------------------------------------------------
+    def moe_route(self, z: torch.Tensor, correction: Optional[torch.Tensor], top: int, idx: torch.Tensor,
+                  wt: torch.Tensor) -> None:
+        """idx[t, :top] = the router outputs with the largest softmax(z[t]) + correction (ties: the lower
+        index), wt = their softmax scores."""
+        _need(z, torch.float32, "router logits", contiguous=False)
+        _need(idx, torch.int32, "chosen experts")
+        _need(wt, torch.float32, "expert weights")
+        T, n_out = z.shape
+        if z.stride(1) != 1 or idx.shape != (T, top) or wt.shape != (T, top):
+            raise KernelError("moe_route: sizes do not match")
+        if correction is not None:
+            _need(correction, torch.float32, "router correction")
+        _check(self._tl_moe_route(_ptr(z), c_int(z.stride(0)), _ptr(correction), c_int(n_out), c_int(top), _ptr(idx),
+                                  _ptr(wt), c_int(T), _stream()), "moe_route")
+
+    def moe_plan(self, idx: torch.Tensor, experts: int, offsets: torch.Tensor, row_token: torch.Tensor,
+                 row_of: torch.Tensor) -> None:
+        """Groups the (token, choice) pairs by expert: offsets [experts + 1], row_token [pairs], row_of
+        [tokens, top] (-1 where the chosen expert has no matrices)."""
+        for t, n in ((idx, "chosen experts"), (offsets, "offsets"), (row_token, "row tokens"), (row_of, "rows")):
+            _need(t, torch.int32, n)
+        T, top = idx.shape
+        if offsets.numel() != experts + 1 or row_token.numel() < T * top or row_of.shape != idx.shape:
+            raise KernelError("moe_plan: sizes do not match")
+        _check(self._tl_moe_plan(_ptr(idx), c_int(T * top), c_int(top), c_int(experts), _ptr(offsets),
+                                 _ptr(row_token), _ptr(row_of), _stream()), "moe_plan")
+
+    def moe_gemm(self, a: torch.Tensor, row_token: Optional[torch.Tensor], w: torch.Tensor, c: torch.Tensor,
+                 offsets: torch.Tensor, up: bool, limit: float = 0.0, alpha: float = 0.0) -> None:
+        """The experts' products over rows grouped by expert.  up: c[row] = act(gate, up) of a[row_token[row]]
+        with w [experts, 2 N, K]; else c[row] (32-bit) = a[row] . w[expert] with w [experts, N, K]."""
+        _need(a, self.act_dtype, "expert input")
+        _need(w, self.act_dtype, "expert matrices")
+        _need(c, self.act_dtype if up else torch.float32, "expert output")
+        E, rows_w, K = w.shape
+        N = rows_w // 2 if up else rows_w
+        if a.shape[1] != K or c.shape[1] != N or offsets.numel() != E + 1 or (up and row_token is None):
+            raise KernelError("moe_gemm: sizes do not match")
+        _check(self._tl_moe_gemm(_ptr(a), c_int(a.stride(0)), _ptr(row_token), _ptr(w), _ptr(c), c_int(c.stride(0)),
+                                 _ptr(offsets), c_int(E), c_int(c.shape[0]), c_int(N), c_int(K), c_int(1 if up else 0),
+                                 c_float(limit), c_float(alpha), _stream()), "moe_gemm")
+
+    def moe_combine(self, yk: torch.Tensor, row_of: torch.Tensor, wt: torch.Tensor, h: torch.Tensor,
+                    out: torch.Tensor, accumulate: bool) -> None:
+        """out[t] (+)= sum_k wt[t, k] * (yk[row_of[t, k]] if row_of[t, k] >= 0 else h[t])."""
+        _need(yk, torch.float32, "expert outputs")
+        _need(row_of, torch.int32, "rows")
+        _need(wt, torch.float32, "expert weights")
+        _need(h, self.act_dtype, "feed-forward input")
+        _need(out, torch.float32, "feed-forward output", contiguous=False)
+        T, top = row_of.shape
+        H = h.shape[1]
+        if out.shape != (T, H) or yk.shape[1] != H or wt.shape != row_of.shape or out.stride(1) != 1:
+            raise KernelError("moe_combine: sizes do not match")
+        _check(self._tl_moe_combine(_ptr(yk), _ptr(row_of), _ptr(wt), _ptr(h), _ptr(out), c_int(out.stride(0)),
+                                    c_int(T), c_int(H), c_int(top), c_int(1 if accumulate else 0), _stream()),
+               "moe_combine")
 
 
 class SamplingOps:

@@ -39,7 +39,9 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
     if spec.embedding_addend is not None:
         out.update(lookup("embedding_addend", spec.embedding_addend.kind).expected_tensors(spec.embedding_addend))
     for layer in spec.layers:
-        _block_class(layer)
+        block_cls = _block_class(layer)
+        if hasattr(block_cls, "expected_tensors"):     # a block with tensors of its own
+            out.update(block_cls.expected_tensors(layer.block, layer.prefix))
         for table, ps, role in (
                 [("mixer", layer.mixer, "mixer"), ("feed_forward", layer.feed_forward, "feed_forward")] +
                 [("norm", ps, role) for role, ps in layer.norms.items()]):
@@ -89,6 +91,10 @@ class DecoderModel:
         self.head: Optional[torch.Tensor] = None
         # a part whose forward reads host-side values of the batch cannot be replayed from a
         # recorded graph; it says so by not setting `graph_safe`
+        multi = [bool(getattr(b, "multi_stream", False)) for b in self.blocks]
+        if any(m != (spec.streams is not None) for m in multi):
+            raise ConfigError("a model with several residual streams needs blocks that take them, and only "
+                              "such a model may use them")
         self.graph_safe = all(getattr(p, "graph_safe", False)
                               for b in self.blocks for p in (b.mixer, b.feed_forward)) and \
             (self.embedding_addend is None or getattr(self.embedding_addend, "graph_safe", False))
@@ -110,6 +116,8 @@ class DecoderModel:
         for b in self.blocks:
             for part in self._parts_of(b):
                 part.load(weights)
+            if hasattr(b, "load"):
+                b.load(weights)
         self.final_norm.load(weights)
         self.head = (self.embedding if self.spec.tie_head_to_embedding
                      else self.rt.matrix(weights[self.spec.head_name]))
@@ -166,6 +174,9 @@ class DecoderModel:
         if self.embedding_addend is not None:
             self.embedding_addend.forward(batch, x)
         order = self.spec.order
+        S = self.spec.streams
+        if S is not None:
+            return self._forward_streams(batch, x, S)
         carry = None
         for k, i in enumerate(order):
             self.mixers[i].bind_cache(self.views[k])
@@ -183,6 +194,33 @@ class DecoderModel:
             return None
         xn = ws.get("head_normed", (batch.n_want, H), rt.act_dtype)
         self.final_norm(x, xn, rows=batch.want_rows)
+        return self._head(batch, xn)
+
+    def _forward_streams(self, batch, x: torch.Tensor, S: int) -> Optional[torch.Tensor]:
+        """The layers over `S` residual streams [tokens, S, hidden], each of which starts as the embedded
+        token; the wanted rows' sum of streams goes to the final norm.  A block may hand the next one its
+        first input already read and normed."""
+        rt, ws = self.rt, self.rt.workspace
+        T, H = batch.n_tokens, self.spec.hidden_size
+        order = self.spec.order
+        xs = ws.get("streams", (T, S, H), torch.float32)
+        rt.ops.stream_spread(x, xs)
+        carry = None
+        for k, i in enumerate(order):
+            self.mixers[i].bind_cache(self.views[k])
+            nxt = self.blocks[order[k + 1]] if k + 1 < len(order) else None
+            carry = self.blocks[i].forward(xs, batch, carry, None, next_block=nxt)
+        self.last_streams = xs
+        if batch.n_want == 0:
+            return None
+        xw = ws.get("streams_sum", (batch.n_want, H), torch.float32)
+        rt.ops.stream_sum(xs, xw, rows=batch.want_rows)
+        xn = ws.get("head_normed", (batch.n_want, H), rt.act_dtype)
+        self.final_norm(xw, xn)
+        return self._head(batch, xn)
+
+    def _head(self, batch, xn: torch.Tensor) -> torch.Tensor:
+        rt, ws = self.rt, self.rt.workspace
         logits = ws.get("logits", (batch.n_want, self.spec.vocab_size), torch.float32)
         self.matmul(xn, self.head, logits, ops.MODE_STORE_F32)
         if self.spec.logit_softcap is not None:

@@ -18,16 +18,21 @@ from .runtime import Runtime
 
 @register_feed_forward("swiglu")
 class SwiGLU:
-    """Parameters: `hidden_size`, `intermediate_size`.  Interface of every
+    """Parameters: `hidden_size`, `intermediate_size`; optionally `tensor_names`, the names of the
+    gate, up and down matrices under the prefix (default: gate_proj.weight, up_proj.weight,
+    down_proj.weight).  Interface of every
     feed-forward: `expected_tensors(spec, prefix)` (a class method), `load(weights)`, and `forward(xn, residual, batch)`,
-    which adds its output to the 32-bit `residual` in place."""
+    which adds its output to the 32-bit `residual` in place (or stores it there with `overwrite=True`,
+    if the part says `can_overwrite`)."""
     graph_safe = True   # forward launches kernels whose arguments do not depend on host values
-
+    can_overwrite = True
+    DEFAULT_NAMES = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
 
     def __init__(self, spec: PartSpec, prefix: str, rt: Runtime):
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
         self.prefix = prefix
+        self.names = tuple(spec.params.get("tensor_names") or self.DEFAULT_NAMES)
         self.rt = rt
         self.matmul = Matmul(rt)
         self.w_gate_up: Optional[torch.Tensor] = None
@@ -36,24 +41,29 @@ class SwiGLU:
     @classmethod
     def expected_tensors(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorSpec]:
         h, i = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        gate, up, down = tuple(spec.params.get("tensor_names") or cls.DEFAULT_NAMES)
         return {
-            f"{prefix}.gate_proj.weight": TensorSpec((i, h)),
-            f"{prefix}.up_proj.weight": TensorSpec((i, h)),
-            f"{prefix}.down_proj.weight": TensorSpec((h, i)),
+            f"{prefix}.{gate}": TensorSpec((i, h)),
+            f"{prefix}.{up}": TensorSpec((i, h)),
+            f"{prefix}.{down}": TensorSpec((h, i)),
         }
 
     def load(self, weights: Dict[str, torch.Tensor]) -> None:
         p = self.prefix
-        self.w_gate_up = self.rt.stack([weights[f"{p}.gate_proj.weight"], weights[f"{p}.up_proj.weight"]])
-        self.w_down = self.rt.matrix(weights[f"{p}.down_proj.weight"])
+        gate, up, down = self.names
+        self.w_gate_up = self.rt.stack([weights[f"{p}.{gate}"], weights[f"{p}.{up}"]])
+        self.w_down = self.rt.matrix(weights[f"{p}.{down}"])
 
     accepts_carry = True   # `xn` may be a NormCarry; `emit` may ask for the next norm's input
 
-    def forward(self, xn, residual: torch.Tensor, batch, emit=None) -> None:
+    def forward(self, xn, residual: torch.Tensor, batch, emit=None, overwrite: bool = False) -> None:
         T = residual.shape[0]
         act = self.rt.workspace.get("ffn_act", (T, self.inter), self.rt.act_dtype)
         self.matmul(xn, self.w_gate_up, act, ops.MODE_SWIGLU)
-        self.matmul(act, self.w_down, residual, ops.MODE_ACCUM_F32, emit=emit)
+        if overwrite:
+            self.matmul(act, self.w_down, residual, ops.MODE_STORE_F32)
+        else:
+            self.matmul(act, self.w_down, residual, ops.MODE_ACCUM_F32, emit=emit)
 
 
 @register_feed_forward("polynorm")

@@ -68,3 +68,31 @@ class ScalarRMSNorm:
     def __call__(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         self.rt.ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
+
+
+@register_norm("rmsnorm_one_plus")
+class OnePlusRMSNorm:
+    """y = x / sqrt(mean(x^2) + eps) * (1 + w): the stored weight lies around zero.  Parameters:
+    `size`, `eps`.  Its tensor is stored under the norm's own name (no `.weight`).  `weight` is
+    the 32-bit factor 1 + w, which is what the row kernel and the stream kernels multiply by."""
+
+    foldable = False
+
+    def __init__(self, spec: PartSpec, prefix: str, rt: Runtime):
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.name = prefix
+        self.rt = rt
+        self.weight: Optional[torch.Tensor] = None
+
+    @classmethod
+    def expected_tensors(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorSpec]:
+        return {prefix: TensorSpec((int(spec.params["size"]),), init=(0.1, 0.0))}
+
+    def load(self, weights: Dict[str, torch.Tensor]) -> None:
+        w = weights[self.name].to(device=self.rt.device, dtype=torch.float32)
+        self.weight = (w + 1.0).contiguous()
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        self.rt.ops.rmsnorm(x, self.weight, self.eps, out, rows)
+        return out

@@ -34,7 +34,8 @@ _INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8, torch.b
 
 @dataclass(frozen=True)
 class TensorSpec:
-    """What a part expects of one tensor: its exact shape, and whether it is a
+    """What a part expects of one tensor: its exact shape (a dimension given as -1 may have any
+    size: the part then takes the size from the stored tensor), and whether it is a
     table of integers.  `init` = (standard deviation, mean) says how random weights draw it
     where the shape alone does not (matrices N(0, 0.02), vectors 1 + N(0, 0.1)).  An
     `optional` tensor may be absent from a folder; if present it is checked like the others
@@ -126,7 +127,7 @@ def check_against(source_name: str, have: Mapping[str, Tuple[Tuple[int, ...], to
         if n not in have:
             continue
         shape, dt = have[n]
-        if tuple(shape) != tuple(spec.shape):
+        if len(shape) != len(spec.shape) or any(w != -1 and int(h) != int(w) for h, w in zip(shape, spec.shape)):
             wrong_shape.append((n, tuple(spec.shape), tuple(shape)))
         if spec.integer != (dt in _INTS):
             wrong_dtype.append((n, str(dt).replace("torch.", "")))

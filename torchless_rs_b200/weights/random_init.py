@@ -160,6 +160,9 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype,
     `dtype` (float32, bfloat16; float16 on the host only).  The same bits on a CUDA device and
     on the host."""
     dev = torch.device(device)
+    if any(int(d) < 0 for d in spec.shape):
+        raise ValueError(f"random weights: tensor '{name}' has a size that only stored weights give; "
+                         "the configuration must state it")
     key = tensor_key(seed, name)
     scale, shift = (NORM_STD, 1.0) if len(spec.shape) == 1 else (MATRIX_STD, 0.0)
     if spec.init is not None:
