@@ -46,7 +46,7 @@ class WindowAttentionBranch:
             keep = mr.integer("keep_first", 0, minimum=0)
         heads, kv = r.integer("heads"), r.integer("kv_heads")
         if heads % kv:
-            raise ConfigError(f"{r.where}: {heads} heads cannot share {kv} key/value heads")
+            raise ConfigError(f"{r.where}: 'heads' {heads} is no multiple of 'kv_heads' {kv}")
         dim = r.integer("dim")
         return cls(heads=heads, kv_heads=kv, dim=dim, vdim=r.integer("vdim", dim), scale=r.number("scale"),
                    softcap=r.number("softcap", None), window=window, keep_first=keep if window else 0)

@@ -26,6 +26,21 @@ from .registry import register_mixer
 from .runtime import Runtime
 
 
+def run_attention(core_ops, q, k_pages, v_pages, gate, sink, out, token_pos, token_seq, seq_slot, page_table,
+                  nh, nkv, dim, vdim, window, keep_first, scale, softcap, batch=None, workspace=None) -> None:
+    """Attention of one step over the pages, by the kernel that takes these sizes: in bfloat16 the
+    tensor-core kernels where they do (key and value sizes that are multiples of 16), else the CUDA-core
+    kernel, which takes every size and is the whole of the 32-bit path.  Which kernel runs changes the
+    order of the sums only."""
+    if q.dtype == torch.bfloat16:
+        from ..csrc import sink_attention_bf16
+        if sink_attention_bf16.run(q, k_pages, v_pages, gate, sink, out, token_pos, token_seq, seq_slot, page_table,
+                                   nh, nkv, dim, vdim, window, keep_first, scale, softcap, batch, workspace):
+            return
+    core_ops.sink_attn(q, k_pages, v_pages, gate, sink, out, token_pos, token_seq, seq_slot, page_table, nh, nkv,
+                       dim, vdim, window, keep_first, scale, softcap)
+
+
 @register_mixer("sink_window_attention")
 class SinkWindowAttention:
     """Parameters: `hidden_size`, `heads`, `kv_heads`, `dim`, `vdim`, `window` (None: all keys),
@@ -52,7 +67,6 @@ class SinkWindowAttention:
         self.rt = rt
         self.matmul = Matmul(rt)
         self.cache = None
-        self.fast = None
 
     @classmethod
     def expected_tensors(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorSpec]:
@@ -102,12 +116,7 @@ class SinkWindowAttention:
                                    batch.token_pos, batch.token_seq, batch.seq_slot, c.page_table, H, G, dim, vdim)
         out = ws.get("swa_out", (T, H * vdim), rt.act_dtype)
         gate = z[:, g_off:]
-        done = False
-        if self.fast is not None:
-            done = self.fast.run(q, c, gate, self.sink, out, batch, H, G, self.window, self.keep_first,
-                                 self.scale, self.softcap, ws)
-        if not done:
-            rt.ops.sink_attn(q, c.k_pages, c.v_pages, gate, self.sink, out, batch.token_pos, batch.token_seq,
-                             batch.seq_slot, c.page_table, H, G, dim, vdim, self.window, self.keep_first,
-                             self.scale, self.softcap)
+        run_attention(rt.ops, q, c.k_pages, c.v_pages, gate, self.sink, out, batch.token_pos, batch.token_seq,
+                      batch.seq_slot, c.page_table, H, G, dim, vdim, self.window, self.keep_first, self.scale,
+                      self.softcap, batch, ws)
         self.matmul(out, self.w_o, residual, ops.MODE_STORE_F32 if overwrite else ops.MODE_ACCUM_F32)
