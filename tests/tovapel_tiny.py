@@ -24,7 +24,7 @@ from plain import tovapel_plain as plain
 
 def left(heads, kv_heads, dim, vdim, window, keep_first=0, scale=None, softcap=None):
     m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
-         "scale": scale if scale is not None else 2.0 / float(np.sqrt(dim))}
+         "scale": scale if scale is not None else 1.0 / float(np.sqrt(dim))}
     if softcap:
         m["softcap"] = softcap
     if window:
@@ -65,7 +65,7 @@ CONFIGS = {
     # no cap, no feed-forward
     "P": config(96, 211, 3, [
         layer(left(3, 1, 16, 24, window=20, keep_first=3, softcap=6.0), right(2, 16, 8, tau=8.0), dense(160)),
-        layer(left(2, 2, 32, 10, window=70, keep_first=1, scale=0.3, softcap=20.0), right(1, 40, 20, tau=3.0),
+        layer(left(2, 2, 32, 10, window=70, keep_first=1, scale=0.15, softcap=20.0), right(1, 40, 20, tau=3.0),
               moe(24, experts=5, identity=2, top=3, limit=0.8)),
         layer(left(4, 2, 8, 8, window=None), right(3, 8, 12, tau=1.0), None),
     ], eps=1e-6, logit_softcap=8.0),
@@ -126,11 +126,13 @@ def make_weights(cfg: dict, seed: int, store: torch.dtype, ranks=(4,) * 16, stat
     for name, shape in tensor_shapes(cfg, ranks).items():
         leaf = name.split(".", 1)[1] if name.startswith("l") else name
         if leaf.endswith(".mix") and "hc" in leaf:
-            v = 0.7 * np.eye(shape[0]) + rng.normal(0, 0.2, shape)
+            v = 0.7 * np.eye(shape[0]) + rng.normal(0, 0.1, shape)
         elif leaf.endswith(".in") and "hc" in leaf:
-            v = rng.normal(1.0 / shape[0], 0.3, shape)
+            # all of one sign: the streams start equal, and a read whose weights cancel would turn the
+            # rounding of the streams into the signal
+            v = rng.uniform(0.5, 1.5, shape) / shape[0]
         elif leaf.endswith(".out") and "hc" in leaf:
-            v = rng.normal(1.0, 0.3, shape)
+            v = rng.uniform(0.5, 1.5, shape) * rng.choice([-1.0, 1.0], shape)
         elif leaf in ("norm1", "norm2", "final.norm"):
             v = rng.normal(0.0, 0.2, shape)                # stored around zero
         elif leaf.endswith(".sink"):
