@@ -280,7 +280,7 @@ def reference_arm(args) -> int:
 
 
 def design_arm(args) -> int:
-    """`--design kikopel`: prefill and decode throughput of the Kikopel design at layer sizes of a real
+    """`--design kikopel|tovapel`: prefill and decode throughput of that design at layer sizes of a real
     model (random weights), beside Mistral (the closest existing model) at equal width, heads, layers,
     feed-forward and window, and every kernel of the design alone against its roofline beside the like
     kernel of the Mistral path.  One JSON line; the default workload is not touched."""
@@ -291,14 +291,18 @@ def design_arm(args) -> int:
     from torchless_rs_b200.sampling.params import SamplingParams
     size, L = args.design_size, args.layers or 8
     T, B, ctx = PREFILL_TOKENS, args.batch or 8, 2048
-    out = {"design": "kikopel", "sizes": dict(measure.KIKOPEL_SIZES[size]), "layers": L, "dtype": "bf16",
+    design = args.design
+    sizes = {"kikopel": measure.KIKOPEL_SIZES, "tovapel": measure.TOVAPEL_SIZES}[design]
+    configs = {"kikopel": (measure.kikopel_config, measure.mistral_like, measure.kikopel_kernels),
+               "tovapel": (measure.tovapel_config, measure.tovapel_like, measure.tovapel_kernels)}[design]
+    out = {"design": design, "sizes": dict(sizes[size]), "layers": L, "dtype": "bf16",
            "data": "synthetic: random weights, fixed token ids", "prefill_tokens": T, "decode_batch": B,
            "decode_context": ctx, "steps": args.steps, "warmup": args.warmup}
     clocks = ClockSampler()
     clocks.start()
     t0 = None
     greedy = SamplingParams.greedy()
-    for name, cfg in (("kikopel", measure.kikopel_config(size, L)), ("mistral", measure.mistral_like(size, L))):
+    for name, cfg in ((design, configs[0](size, L)), ("mistral", configs[1](size, L))):
         model = tl.from_random(config_from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=B * (ctx + 64),
                                max_batch=B, max_seq_len=ctx + 64)
         eng = model.engine
@@ -327,7 +331,7 @@ def design_arm(args) -> int:
                      "decode_tok_s": round(B / (ms / 1e3), 1), "weight_bytes": eng.model.weight_bytes()}
         del model, eng
         torch.cuda.empty_cache()
-    out["kernels"] = measure.kikopel_kernels(size, T, B, ctx, 24, file=sys.stderr)
+    out["kernels"] = configs[2](size, T, B, ctx, 24, file=sys.stderr)
     clocks.stop()
     out["clocks"] = clocks.summary(t0, clocks.mark())
     print(json.dumps(out))
@@ -336,7 +340,7 @@ def design_arm(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["kikopel"],
+    ap.add_argument("--design", default=None, choices=["kikopel", "tovapel"],
                     help="measure another design beside Mistral at equal sizes instead of the default workload")
     ap.add_argument("--design-size", default="1b", choices=["1b", "7b"])
     ap.add_argument("--gpus", type=int, default=1)

@@ -4,3 +4,4 @@ model first needs it)."""
 from . import build  # noqa: F401
 from . import gemm_bf16  # noqa: F401
 from . import attention_bf16  # noqa: F401
+from . import sink_attention_bf16  # noqa: F401

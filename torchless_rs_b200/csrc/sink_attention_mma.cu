@@ -1,0 +1,465 @@
+// bfloat16 kernels of the attention with a sink, capped scores and a window that keeps the first keys
+// (what it computes: sink_attention.cu), for one pair of key and value sizes per library
+// (-DSA_DIM, -DSA_VDIM, multiples of 16 up to 128).
+//
+//   sink_attn_mma_kernel     steps of many tokens: a block takes 64 consecutive tokens of one sequence
+//                            and one query head; keys and values come page by page (64 keys) into
+//                            shared memory with cp.async, two pages in flight; Q K^T and P V on the
+//                            tensor cores (mma.sync m16n8k16, fragments by ldmatrix from swizzled
+//                            tiles: a key page is the B operand as it lies, and so is the transposed
+//                            value page); scores, cap, mask, running maximum and sum in 32-bit
+//                            registers; the sink opens maximum and sum; the gate and 1/sum close.
+//   sink_attn_split_kernel   steps of few tokens (decode): a block takes one token, one key/value head
+//                            and a share of its pages, all query heads of the group at once (the
+//                            pages are read once for the group); 8 lanes per key for the scores, a
+//                            thread per value entry for the weighted sum; partial maximum, sum and
+//                            output go to a buffer,
+//   sink_attn_merge_kernel   which joins the shares, counts the sink once and applies the gate.
+//
+// The pages a query tile needs: those of the kept first keys that lie before the window's first
+// page, then the window's pages up to the tile's last position; the exact visibility is a mask
+// on every score: j <= i and (i - j < window or j < keep_first).
+#include "common.cuh"
+#include <mma.h>
+
+#ifndef SA_DIM
+#error "SA_DIM and SA_VDIM (key and value sizes) must be given by the build"
+#endif
+#if TL_DTYPE != 1
+#error "the tensor-core attention is built for bfloat16 only"
+#endif
+
+constexpr int DIM = SA_DIM, VDIM = SA_VDIM;
+constexpr int BM = 64, BN = TL_PAGE, THREADS = 128;
+static_assert(TL_PAGE == 64, "a page is one key tile of 64");
+static_assert(DIM % 16 == 0 && VDIM % 16 == 0 && DIM >= 16 && VDIM >= 16 && DIM <= 128 && VDIM <= 128, "sizes");
+#define LOG2E 1.4426950408889634f
+
+typedef __nv_bfloat16 bf16;
+
+// 16-byte chunks of a row are permuted so that the eight rows an ldmatrix reads fall into eight
+// different banks groups: for rows of R elements, chunk c of row r lies at chunk c ^ f(r).
+template <int R>
+__device__ __forceinline__ int swz(int row, int chunk) {
+  constexpr int C = R / 8;
+  if (C % 8 == 0) return chunk ^ (row & 7);
+  if (C == 4) return chunk ^ ((row >> 1) & 3);
+  if (C % 4 == 0) return chunk ^ (row & 3);
+  if (C % 2 == 0) return chunk ^ (row & 1);
+  return chunk;
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+// tanh through one exponential: 1 - 2 / (e^(2x) + 1); exact limits at both ends
+__device__ __forceinline__ float tanh_fast(float x) {
+  const float e = __expf(2.0f * x);
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+
+// A tile's rows of R elements, contiguous in global memory, into a swizzled shared tile.
+template <int R, int ROWS>
+__device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, int tid) {
+  constexpr int C = R / 8;
+  for (int i = tid; i < ROWS * C; i += THREADS) {
+    const int row = i / C, chunk = i - row * C;
+    cp_async16(dst + row * R + swz<R>(row, chunk) * 8, src + (size_t)i * 8);
+  }
+}
+
+struct TilePages {
+  int n_kept, first_col, n_iter;
+  __device__ __forceinline__ int col(int i) const { return i < n_kept ? i : first_col + (i - n_kept); }
+};
+// The page-table columns that queries at positions p_first .. p_last need.
+__device__ __forceinline__ TilePages tile_pages(int p_first, int p_last, int window, int keep_first) {
+  TilePages t;
+  const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  t.first_col = lo / TL_PAGE;
+  t.n_kept = 0;
+  if (keep_first > 0 && t.first_col > 0) {
+    const int last_kept = (keep_first - 1) / TL_PAGE;
+    t.n_kept = (last_kept < t.first_col - 1 ? last_kept : t.first_col - 1) + 1;
+  }
+  t.n_iter = t.n_kept + (p_last / TL_PAGE - t.first_col + 1);
+  return t;
+}
+
+__global__ void __launch_bounds__(THREADS)
+sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                     const float* __restrict__ gate, int ldg, const float* __restrict__ sink,
+                     bf16* __restrict__ out, const int* __restrict__ token_pos, const int* __restrict__ seq_start,
+                     const int* __restrict__ seq_slot, const int* __restrict__ page_table, int table_stride,
+                     int n_seqs, int nh, int nkv, int window, int keep_first, float scale, float cap) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);               // [BM][DIM]
+  bf16* Ks = Qs + BM * DIM;                                    // [2][BN][DIM]
+  bf16* Vs = Ks + 2 * BN * DIM;                                // [2][VDIM][BN]
+  __shared__ int tile_info[3];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int h = blockIdx.y, kvh = h / (nh / nkv);
+  if (tid == 0) {
+    int tile = blockIdx.x, found = -1, b = 0;
+    for (; b < n_seqs; ++b) {
+      const int cnt = seq_start[b + 1] - seq_start[b];
+      const int tiles = (cnt + BM - 1) / BM;
+      if (tile < tiles) { found = b; break; }
+      tile -= tiles;
+    }
+    tile_info[0] = found;
+    if (found >= 0) {
+      tile_info[1] = seq_start[found] + tile * BM;
+      const int left = seq_start[found + 1] - tile_info[1];
+      tile_info[2] = left < BM ? left : BM;
+    }
+  }
+  __syncthreads();
+  const int b = tile_info[0];
+  if (b < 0) return;
+  const int t0 = tile_info[1], rows = tile_info[2];
+  const int p_first = token_pos[t0], p_last = p_first + rows - 1;
+  const int* table = page_table + (size_t)seq_slot[b] * table_stride;
+  const TilePages tp = tile_pages(p_first, p_last, window, keep_first);
+
+  // Q tile (rows beyond the sequence's end are zero) and the first page
+  {
+    constexpr int C = DIM / 8;
+    for (int i = tid; i < BM * C; i += THREADS) {
+      const int row = i / C, chunk = i - row * C;
+      bf16* dst = Qs + row * DIM + swz<DIM>(row, chunk) * 8;
+      if (row < rows) cp_async16(dst, q + ((size_t)(t0 + row) * nh + h) * DIM + chunk * 8);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  auto load_page = [&](int it, int buf) {
+    const int page = table[tp.col(it)];
+    load_tile_async<DIM, BN>(Ks + buf * BN * DIM, k_pages + ((size_t)page * nkv + kvh) * BN * DIM, tid);
+    load_tile_async<BN, VDIM>(Vs + buf * VDIM * BN, v_pages + ((size_t)page * nkv + kvh) * VDIM * BN, tid);
+  };
+  load_page(0, 0);
+  cp_async_commit();
+
+  const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;          // the two rows this thread holds
+  const int pos0 = r0 < rows ? p_first + r0 : -1, pos1 = r1 < rows ? p_first + r1 : -1;
+  const float sk = sink != nullptr ? sink[h] * LOG2E : -INFINITY;
+  float m0 = sk, m1 = sk;
+  float l0 = sink != nullptr ? 1.0f : 0.0f, l1 = l0;
+  float o[VDIM / 8][4];
+#pragma unroll
+  for (int n = 0; n < VDIM / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+  unsigned qf[DIM / 16][4];
+  const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
+  const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
+
+  for (int it = 0; it < tp.n_iter; ++it) {
+    const int buf = it & 1;
+    if (it + 1 < tp.n_iter) load_page(it + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (it == 0) {
+#pragma unroll
+      for (int kk = 0; kk < DIM / 16; ++kk) {
+        const int row = warp * 16 + (lane & 15), chunk = kk * 2 + (lane >> 4);
+        ldmatrix_x4(qf[kk], Qs + row * DIM + swz<DIM>(row, chunk) * 8);
+      }
+    }
+    const bf16* Kb = Ks + buf * BN * DIM;
+    const bf16* Vb = Vs + buf * VDIM * BN;
+    const int key0 = tp.col(it) * TL_PAGE;
+    // S = Q K^T : 16 rows x 64 keys per warp
+    float s[BN / 8][4];
+#pragma unroll
+    for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < DIM / 16; ++kk) {
+#pragma unroll
+      for (int np = 0; np < BN / 16; ++np) {
+        unsigned bfr[4];
+        const int row = np * 16 + (lane >> 4) * 8 + (lane & 7), chunk = kk * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(bfr, Kb + row * DIM + swz<DIM>(row, chunk) * 8);
+        mma_bf16(s[2 * np], qf[kk], bfr[0], bfr[1]);
+        mma_bf16(s[2 * np + 1], qf[kk], bfr[2], bfr[3]);
+      }
+    }
+    // scale, cap, mask; the page's row maxima
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = key0 + n * 8 + (lane & 3) * 2 + (e & 1);
+        const int i = e < 2 ? pos0 : pos1;
+        float v = cap > 0.0f ? cap2 * tanh_fast(s[n][e] * scale * inv_cap) : s[n][e] * scale2;
+        const bool vis = j <= i && (window <= 0 || i - j < window || j < keep_first);
+        v = vis ? v : -INFINITY;
+        s[n][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    // (a row that has seen nothing yet and has no sink keeps -inf: its factors are taken as zero)
+    const float a0 = n0 == -INFINITY ? 0.0f : exp2f(m0 - n0), a1 = n1 == -INFINITY ? 0.0f : exp2f(m1 - n1);
+    const float b0 = n0 == -INFINITY ? 0.0f : n0, b1 = n1 == -INFINITY ? 0.0f : n1;
+    float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+    for (int n = 0; n < BN / 8; ++n) {
+      s[n][0] = exp2f(s[n][0] - b0); s[n][1] = exp2f(s[n][1] - b0);
+      s[n][2] = exp2f(s[n][2] - b1); s[n][3] = exp2f(s[n][3] - b1);
+      sum0 += s[n][0] + s[n][1];
+      sum1 += s[n][2] + s[n][3];
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    l0 = l0 * a0 + sum0; l1 = l1 * a1 + sum1;
+    m0 = n0; m1 = n1;
+#pragma unroll
+    for (int n = 0; n < VDIM / 8; ++n) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+    // O += P V : P from the score registers, V^T rows are the B operand
+#pragma unroll
+    for (int kk = 0; kk < BN / 16; ++kk) {
+      unsigned pa[4];
+      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < VDIM / 16; ++np) {
+        unsigned bfr[4];
+        const int row = np * 16 + (lane >> 4) * 8 + (lane & 7), chunk = kk * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(bfr, Vb + row * BN + swz<BN>(row, chunk) * 8);
+        mma_bf16(o[2 * np], pa, bfr[0], bfr[1]);
+        mma_bf16(o[2 * np + 1], pa, bfr[2], bfr[3]);
+      }
+    }
+    __syncthreads();   // the buffer is refilled two iterations on
+  }
+  cp_async_wait<0>();
+  float f0 = 0.0f, f1 = 0.0f;
+  if (r0 < rows) f0 = (gate != nullptr ? 1.0f / (1.0f + __expf(-gate[(size_t)(t0 + r0) * ldg + h])) : 1.0f) / l0;
+  if (r1 < rows) f1 = (gate != nullptr ? 1.0f / (1.0f + __expf(-gate[(size_t)(t0 + r1) * ldg + h])) : 1.0f) / l1;
+#pragma unroll
+  for (int n = 0; n < VDIM / 8; ++n) {
+    const int c = n * 8 + (lane & 3) * 2;
+    if (r0 < rows)
+      *reinterpret_cast<unsigned*>(out + ((size_t)(t0 + r0) * nh + h) * VDIM + c) = pack_bf16(o[n][0] * f0, o[n][1] * f0);
+    if (r1 < rows)
+      *reinterpret_cast<unsigned*>(out + ((size_t)(t0 + r1) * nh + h) * VDIM + c) = pack_bf16(o[n][2] * f1, o[n][3] * f1);
+  }
+}
+
+extern "C" int tl_sink_attn_mma(const void* q, const void* k_pages, const void* v_pages, const float* gate, int ldg,
+                                const float* sink, void* out, const int* token_pos, const int* seq_start,
+                                const int* seq_slot, const int* page_table, int table_stride, int T, int n_seqs,
+                                int nh, int nkv, int window, int keep_first, float scale, float cap,
+                                cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh > 65535) return TL_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)(BM * DIM + 2 * BN * DIM + 2 * VDIM * BN) * sizeof(bf16);
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(sink_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return TL_ERR_UNSUPPORTED;
+    set = true;
+  }
+  const int tiles = (T + BM - 1) / BM + n_seqs;      // an upper bound; a block without a tile leaves
+  return tl_launch(sink_attn_mma_kernel, dim3(tiles, nh), dim3(THREADS), smem, stream, (const bf16*)q,
+                   (const bf16*)k_pages, (const bf16*)v_pages, gate, ldg, sink, (bf16*)out, token_pos, seq_start,
+                   seq_slot, page_table, table_stride, n_seqs, nh, nkv, window, keep_first, scale, cap);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Steps of few tokens.  part: [T][nkv][splits][group][VDIM + 2] floats: output sums, then maximum (log2
+// units) and sum of the share; a share without visible keys leaves maximum -inf and sum 0.
+// ---------------------------------------------------------------------------------------------------
+#define SPLIT_MAX_GROUP 8
+
+__global__ void __launch_bounds__(THREADS)
+sink_attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                       float* __restrict__ part, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
+                       const int* __restrict__ seq_slot, const int* __restrict__ page_table, int table_stride, int nh,
+                       int nkv, int window, int keep_first, float scale, float cap, int splits) {
+  __shared__ float qs[SPLIT_MAX_GROUP][DIM];
+  __shared__ float sc[SPLIT_MAX_GROUP][BN];
+  __shared__ float alpha_s[SPLIT_MAX_GROUP], m_s[SPLIT_MAX_GROUP], l_s[SPLIT_MAX_GROUP];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = nh / nkv;
+  const int pos = token_pos[t];
+  const int* table = page_table + (size_t)seq_slot[token_seq[t]] * table_stride;
+  const TilePages tp = tile_pages(pos, pos, window, keep_first);
+  const int per = (tp.n_iter + splits - 1) / splits;
+  const int i0 = sp * per, i1 = (i0 + per < tp.n_iter) ? i0 + per : tp.n_iter;
+  for (int i = tid; i < group * DIM; i += THREADS)
+    qs[i / DIM][i % DIM] = __bfloat162float(q[((size_t)t * nh + kvh * group) * DIM + i]);
+  if (tid < SPLIT_MAX_GROUP) { m_s[tid] = -INFINITY; l_s[tid] = 0.0f; }
+  __syncthreads();
+  float acc[SPLIT_MAX_GROUP];
+#pragma unroll
+  for (int g = 0; g < SPLIT_MAX_GROUP; ++g) acc[g] = 0.0f;
+  const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
+  const int sub = lane & 7, kq = lane >> 3;             // 8 lanes share a key; a warp takes 4 keys at a time
+  for (int it = i0; it < i1; ++it) {
+    const int col = tp.col(it);
+    const int page = table[col];
+    const bf16* kb = k_pages + ((size_t)page * nkv + kvh) * BN * DIM;
+    // scores of the page's 64 keys for every head of the group
+    for (int kbase = warp * 16; kbase < warp * 16 + 16; kbase += 4) {
+      const int key = kbase + kq;
+      float dot[SPLIT_MAX_GROUP];
+#pragma unroll
+      for (int g = 0; g < SPLIT_MAX_GROUP; ++g) dot[g] = 0.0f;
+      for (int c = sub; c < DIM / 8; c += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(kb + (size_t)key * DIM + c * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float kv[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); kv[2 * e] = f.x; kv[2 * e + 1] = f.y; }
+#pragma unroll
+        for (int g = 0; g < SPLIT_MAX_GROUP; ++g)
+          if (g < group) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dot[g] = fmaf(qs[g][c * 8 + e], kv[e], dot[g]);
+          }
+      }
+#pragma unroll
+      for (int g = 0; g < SPLIT_MAX_GROUP; ++g)
+        if (g < group) {
+          float d = dot[g];
+          d += __shfl_xor_sync(0xffffffffu, d, 1);
+          d += __shfl_xor_sync(0xffffffffu, d, 2);
+          d += __shfl_xor_sync(0xffffffffu, d, 4);
+          if (sub == 0) {
+            const int j = col * TL_PAGE + key;
+            float v = d * scale;
+            if (cap > 0.0f) v = cap * tanhf(v * inv_cap);
+            const bool vis = j <= pos && (window <= 0 || pos - j < window || j < keep_first);
+            sc[g][key] = vis ? v * LOG2E : -INFINITY;
+          }
+        }
+    }
+    __syncthreads();
+    // running maximum and sum per head; the scores become weights
+    for (int g = warp; g < group; g += THREADS / 32) {
+      const float s0 = sc[g][lane], s1 = sc[g][lane + 32];
+      const float mx = warp_max(fmaxf(s0, s1));
+      const float m_old = m_s[g];
+      const float m_new = fmaxf(m_old, mx);
+      const float base = m_new == -INFINITY ? 0.0f : m_new;
+      const float p0 = exp2f(s0 - base), p1 = exp2f(s1 - base);
+      const float sum = warp_sum(p0 + p1);
+      sc[g][lane] = p0;
+      sc[g][lane + 32] = p1;
+      if (lane == 0) {
+        const float a = m_new == -INFINITY ? 0.0f : exp2f(m_old - m_new);
+        alpha_s[g] = a;
+        l_s[g] = l_s[g] * a + sum;
+        m_s[g] = m_new;
+      }
+    }
+    __syncthreads();
+    if (tid < VDIM) {
+      const bf16* vb = v_pages + (((size_t)page * nkv + kvh) * VDIM + tid) * BN;
+#pragma unroll
+      for (int g = 0; g < SPLIT_MAX_GROUP; ++g) acc[g] *= g < group ? alpha_s[g] : 0.0f;
+#pragma unroll
+      for (int c = 0; c < BN / 8; ++c) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(vb + c * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float vv[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); vv[2 * e] = f.x; vv[2 * e + 1] = f.y; }
+#pragma unroll
+        for (int g = 0; g < SPLIT_MAX_GROUP; ++g)
+          if (g < group) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g] = fmaf(sc[g][c * 8 + e], vv[e], acc[g]);
+          }
+      }
+    }
+    __syncthreads();   // sc is rewritten by the next page
+  }
+  float* dst = part + ((((size_t)t * nkv + kvh) * splits + sp) * group) * (VDIM + 2);
+#pragma unroll
+  for (int g = 0; g < SPLIT_MAX_GROUP; ++g)
+    if (g < group) {
+      if (tid < VDIM) dst[(size_t)g * (VDIM + 2) + tid] = acc[g];
+      if (tid == 0) {
+        dst[(size_t)g * (VDIM + 2) + VDIM] = m_s[g];
+        dst[(size_t)g * (VDIM + 2) + VDIM + 1] = l_s[g];
+      }
+    }
+}
+
+__global__ void __launch_bounds__(THREADS)
+sink_attn_merge_kernel(const float* __restrict__ part, const float* __restrict__ gate, int ldg,
+                       const float* __restrict__ sink, bf16* __restrict__ out, int nh, int nkv, int splits) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int group = nh / nkv, kvh = h / group, g = h - kvh * group;
+  const float* src = part + (((size_t)t * nkv + kvh) * splits * group + g) * (VDIM + 2);
+  const size_t stride = (size_t)group * (VDIM + 2);
+  float m = sink != nullptr ? sink[h] * LOG2E : -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, src[s * stride + VDIM]);
+  float l = sink != nullptr ? exp2f(sink[h] * LOG2E - m) : 0.0f;
+  float a = 0.0f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = src[s * stride + VDIM];
+    const float w = ms == -INFINITY ? 0.0f : exp2f(ms - m);
+    l += src[s * stride + VDIM + 1] * w;
+    if (tid < VDIM) a += src[s * stride + tid] * w;
+  }
+  const float gv = gate != nullptr ? 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h])) : 1.0f;
+  if (tid < VDIM) out[((size_t)t * nh + h) * VDIM + tid] = __float2bfloat16_rn(a * gv / l);
+}
+
+extern "C" long long tl_sink_attn_split_floats(int T, int nh, int nkv, int splits) {
+  return (long long)T * nkv * splits * (nh / nkv) * (VDIM + 2);
+}
+
+extern "C" int tl_sink_attn_split(const void* q, const void* k_pages, const void* v_pages, const float* gate, int ldg,
+                                  const float* sink, void* out, float* part, const int* token_pos,
+                                  const int* token_seq, const int* seq_slot, const int* page_table,
+                                  int table_stride, int T, int nh, int nkv, int window, int keep_first, float scale,
+                                  float cap, int splits, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > SPLIT_MAX_GROUP || nh > 65535 || nkv > 65535 || splits < 1 ||
+      splits > 65535 || part == nullptr)
+    return TL_ERR_UNSUPPORTED;
+  const int rc = tl_launch(sink_attn_split_kernel, dim3(T, nkv, splits), dim3(THREADS), 0, stream, (const bf16*)q,
+                           (const bf16*)k_pages, (const bf16*)v_pages, part, token_pos, token_seq, seq_slot,
+                           page_table, table_stride, nh, nkv, window, keep_first, scale, cap, splits);
+  if (rc != 0) return rc;
+  return tl_launch(sink_attn_merge_kernel, dim3(T, nh), dim3(THREADS), 0, stream, (const float*)part, gate, ldg,
+                   sink, (bf16*)out, nh, nkv, splits);
+}

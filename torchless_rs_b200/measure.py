@@ -316,6 +316,191 @@ def kikopel_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) 
     return rows
 
 
+# Layer sizes at which the Tovapel kernels are measured: the width, heads and feed-forward of a 1B- and a
+# 7B-class decoder; four residual streams; attention with a quarter as many key/value heads, a window of 4096
+# that keeps the first four keys; gated linear attention with keys of half and values of the full width;
+# every other layer sixteen experts of a quarter of the dense inner size, four chosen, two pass-through outputs.
+TOVAPEL_SIZES = {
+    "1b": dict(width=2048, streams=4, heads=16, kv_heads=4, dim=128, vdim=128, window=4096, keep_first=4, ff=5632,
+               r_heads=16, r_dim=64, r_vdim=128, rank=16, experts=16, identity=2, top=4, e_ff=1408, vocab=32000),
+    "7b": dict(width=4096, streams=4, heads=32, kv_heads=8, dim=128, vdim=128, window=4096, keep_first=4, ff=14336,
+               r_heads=32, r_dim=64, r_vdim=128, rank=16, experts=16, identity=2, top=4, e_ff=3584, vocab=32000),
+}
+
+
+def tovapel_config(size: str, layers: int) -> dict:
+    """config.json of a Tovapel model of `layers` layers at these sizes: dense and expert feed-forwards in turn."""
+    z = TOVAPEL_SIZES[size]
+    mixer = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                      "scale": 1.0 / math.sqrt(z["dim"]), "softcap": 50.0,
+                      "mask": {"size": z["window"], "keep_first": z["keep_first"]}},
+             "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "tau": 16.0, "rank": z["rank"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["e_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"]}}
+    return {"architecture": "Tovapel", "width": z["width"], "vocab": z["vocab"], "streams": z["streams"],
+            "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "max_position_embeddings": 32768,
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": moe if i % 2 else dense} for i in range(layers)]}
+
+
+def tovapel_like(size: str, layers: int) -> dict:
+    """The closest existing model at equal size: Mistral with the same width, heads, key/value heads,
+    feed-forward and window."""
+    z = TOVAPEL_SIZES[size]
+    return dict(MISTRAL_7B_SIZES, num_hidden_layers=layers, hidden_size=z["width"], num_attention_heads=z["heads"],
+                num_key_value_heads=z["kv_heads"], head_dim=128, intermediate_size=z["ff"],
+                vocab_size=z["vocab"], sliding_window=z["window"], max_position_embeddings=32768)
+
+
+def tovapel_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) -> list:
+    """Every kernel of the Tovapel design alone at the sizes `size`, for a prompt of T tokens and for a decode
+    step of B sequences at a context of `ctx`, beside the like kernel of an existing model at equal sizes.
+    Rows and roofline as `kikopel_kernels` defines them."""
+    import json
+    import os
+    from .csrc import ops
+    from .csrc.attention_bf16 import AttentionBf16
+    from .csrc.gemm_bf16 import GemmBf16
+    from .parts.runtime import Workspace
+    from .parts.sink_attention import run_attention
+    z = TOVAPEL_SIZES[size]
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    pk = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.isfile(pk):
+        peaks.update(json.load(open(pk)))
+    o = ops.core_ops(torch.bfloat16)
+    dev, bf = "cuda", torch.bfloat16
+    H, G, dim, vdim, W, S = z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["width"], z["streams"]
+    rows = []
+
+    def report(name, case, us, byts, flops):
+        t_mem, t_fl = byts / (peaks["hbm_gbs"] * 1e3), flops / (peaks["bf16_tflops"] * 1e6)     # microseconds
+        frac = max(t_mem, t_fl) / us
+        rows.append({"kernel": name, "case": case, "us": round(us, 2), "roofline_frac": round(frac, 4),
+                     "bound": "memory" if t_mem >= t_fl else "tensor"})
+        print(f"{name:30s} {case:22s} {us:10.2f} us   {frac:7.4f} of the roofline ({rows[-1]['bound']})", file=file)
+
+    ws = Workspace(torch.device("cuda"))
+    for case, n_tok, seqs, past in ((f"prompt {T}", T, 1, 0), (f"decode {B} x {ctx}", B, B, ctx - 1)):
+        per = n_tok // seqs
+        few = max(2, iters // 8) if n_tok > 64 else iters
+        pos = torch.cat([torch.arange(past, past + per, dtype=torch.int32) for _ in range(seqs)]).to(dev)
+        seq = torch.arange(seqs, dtype=torch.int32).repeat_interleave(per).to(dev)
+        start = (torch.arange(seqs + 1, dtype=torch.int32) * per).to(dev)
+        seen = sum(min(p + 1, z["window"] + z["keep_first"]) for p in range(past, past + per)) * seqs
+        kp, vp, table, slot = _paged(seqs, past + per, G, dim)
+        lens = torch.full((seqs,), past + per, dtype=torch.int32, device=dev)
+        # --- attention with sink, cap and kept first keys, beside Mistral's attention at equal heads
+        q = torch.randn((n_tok, H * dim), device=dev, dtype=bf)
+        out = torch.empty((n_tok, H * vdim), device=dev, dtype=bf)
+        gate, sink = torch.randn((n_tok, H), device=dev), torch.zeros(H, device=dev)
+
+        class _B:      # what the kernel choice reads of a step
+            n_tokens, n_seqs, is_decode, max_len, seq_start, seq_len, seq_slot = n_tok, seqs, per == 1, past + per, start, lens, slot
+        us = _time(lambda: run_attention(o, q, kp, vp, gate, sink, out, pos, seq, slot, table, H, G, dim, vdim,
+                                         z["window"], z["keep_first"], 0.088, 50.0, _B, ws), few)
+        cache_b = 2.0 * seqs * min(past + per, z["window"]) * G * (dim + vdim)
+        report("sink_attn", case, us, cache_b + n_tok * H * (dim + vdim) * 2.0, 2.0 * H * (dim + vdim) * seen)
+        att = AttentionBf16.get(128)
+        om = torch.empty_like(q)
+        if seqs == 1:
+            us = _time(lambda: att.prefill(q, kp, vp, om, start, lens, slot, table, 1, n_tok, H, G, z["window"],
+                                           0.088, variant="tc"), iters)
+        else:
+            from .csrc import attention_bf16
+            n = attention_bf16.decode_splits(seqs, G, past + per, z["window"])
+            us = _time(lambda: att.decode(q, kp, vp, om, lens, slot, table, H, G, z["window"], 0.088, n, ws), iters)
+        report("  like: attention (Mistral)", case, us, cache_b + n_tok * H * 128 * 4.0, 4.0 * H * 128 * seen)
+        # --- bias, query/key norm and cache write, beside Mistral's rotation + cache write
+        cols = (H + G) * dim + G * vdim
+        zq = torch.randn((n_tok, cols + H), device=dev)
+        bias, wn = torch.zeros(cols, device=dev), torch.ones(dim, device=dev)
+        us = _time(lambda: o.qk_norm_cache_write(zq, bias, wn, wn, 1e-5, q, kp, vp, pos, seq, slot, table, H, G, dim,
+                                                 vdim), iters)
+        report("qk_norm_cache_write", case, us, n_tok * cols * 6.0, 0.0)
+        qkv = torch.randn((n_tok, (H + 2 * G) * 128), device=dev)
+        inv128 = torch.tensor([1e6 ** (-i / 64.0) for i in range(64)], device=dev)
+        us = _time(lambda: o.rope_cache_write(qkv, q, kp, vp, pos, seq, slot, table, inv128, 0, H, G, 128), iters)
+        report("  like: rope_cache_write", case, us, n_tok * (H + 2 * G) * 128 * 6.0, 0.0)
+        # --- the two recurrences: this design's beside the gated scan of the Kikopel path at equal state
+        rh, rd, rv = z["r_heads"], z["r_dim"], z["r_vdim"]
+        zz = torch.randn((n_tok, 2 * rh * rd + 2 * rh * rv), device=dev)
+        za = torch.randn((n_tok, rh * rd), device=dev) + 3.0
+        state = torch.zeros((seqs, rh, rd, rv), device=dev)
+        so = torch.empty((n_tok, rh * rv), device=dev)
+        ab = torch.zeros(rh * rd, device=dev)
+        hd, hv = rh * rd, rh * rv
+        us = _time(lambda: o.gla_scan(zz[:, :hd], zz[:, hd:2 * hd], zz[:, 2 * hd:2 * hd + hv], za, ab, 16.0, 0.125,
+                                      state, so, start, slot, rh, rd, rv), few)
+        scan_b = n_tok * (3 * hd + 2 * hv) * 4.0 + seqs * hd * rv * 8.0
+        report("gla_scan", case, us, scan_b, 4.0 * n_tok * hd * rv)
+        z2 = torch.randn((n_tok, 2 * hd + hv), device=dev)
+        low = torch.full((hd,), 0.5, device=dev)
+        state.zero_()
+        us = _time(lambda: o.gated_scan(z2, ab, low, state, so, start, slot, rh, rd, rv, workspace=ws), few)
+        report("  like: gated_scan (Kikopel)", case, us, n_tok * (2 * hd + 2 * hv) * 4.0 + seqs * hd * rv * 8.0,
+               4.0 * n_tok * hd * rv)
+        gated = torch.empty((n_tok, hv), device=dev, dtype=bf)
+        nw = torch.ones(rv, device=dev)
+        us = _time(lambda: o.headnorm_silu_gate(so, nw, 1e-5, zz[:, 2 * hd + hv:], gated, rh, rv), iters)
+        report("headnorm_silu_gate", case, us, n_tok * hv * 10.0, 0.0)
+        # --- the streams, the branch norms, beside Mistral's norm kernel
+        xs = torch.randn((n_tok, S, W), device=dev)
+        y = torch.randn((n_tok, W), device=dev)
+        a, b, M = torch.ones(S, device=dev) / S, torch.ones(S, device=dev), torch.eye(S, device=dev)
+        w32 = torch.ones(W, device=dev)
+        xb = torch.empty((n_tok, W), device=dev, dtype=bf)
+        us = _time(lambda: o.hc_read_norm(xs, a, w32, 1e-5, xb), iters)
+        report("hc_read_norm", case, us, n_tok * W * (4.0 * S + 2.0), 0.0)
+        us = _time(lambda: o.hc_write(xs, M, b, y, next_read=(a, w32, 1e-5, xb)), iters)
+        report("hc_write (+ next read, norm)", case, us, n_tok * W * (8.0 * S + 6.0), 0.0)
+        y2 = torch.randn((n_tok, W), device=dev)
+        x = torch.randn((n_tok, W), device=dev)
+        us = _time(lambda: o.branch_norm_mean([y, y2], [w32, w32], 1e-5, x, accumulate=False), iters)
+        report("branch_norm_mean", case, us, n_tok * W * 12.0, 0.0)
+        wb = torch.ones(W, device=dev, dtype=bf)
+        us = _time(lambda: o.rmsnorm(x, wb, 1e-5, xb), iters)
+        report("  like: rmsnorm", case, us, n_tok * W * 6.0, 0.0)
+        # --- the experts: choice and grouping, the two grouped products, the weighted sum; beside the
+        # tensor-core product of the same FLOPs (all pairs through one expert's matrices)
+        E, I, top, f = z["experts"], z["identity"], z["top"], z["e_ff"]
+        zr = torch.randn((n_tok, E + I), device=dev)
+        idx = torch.empty((n_tok, top), dtype=torch.int32, device=dev)
+        wt = torch.empty((n_tok, top), device=dev)
+        corr = torch.zeros(E + I, device=dev)
+        off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        row_token = torch.empty(n_tok * top, dtype=torch.int32, device=dev)
+        row_of = torch.empty((n_tok, top), dtype=torch.int32, device=dev)
+
+        def choose():
+            o.moe_route(zr, corr, top, idx, wt)
+            o.moe_plan(idx, E, off, row_token, row_of)
+        us = _time(choose, iters)
+        report("moe_route + moe_plan", case, us, n_tok * ((E + I) * 4.0 + top * 20.0), 0.0)
+        xn = torch.randn((n_tok, W), device=dev, dtype=bf)
+        w_up = torch.randn((E, 2 * f, W), device=dev, dtype=bf) * 0.02
+        w_dn = torch.randn((E, W, f), device=dev, dtype=bf) * 0.02
+        act = torch.empty((n_tok * top, f), device=dev, dtype=bf)
+        yk = torch.empty((n_tok * top, W), device=dev)
+        pairs = n_tok * top * E / (E + I)              # expected rows of real experts
+        used = min(E, n_tok * top)                     # experts whose matrices a step must read
+        us = _time(lambda: o.moe_gemm(xn, row_token, w_up, act, off, up=True, limit=7.0, alpha=1.702), few)
+        report("moe_gemm (gate, up, act)", case, us, used * 2 * f * W * 2.0 + pairs * (W + f) * 2.0, 4.0 * pairs * f * W)
+        us = _time(lambda: o.moe_gemm(act, None, w_dn, yk, off, up=False), few)
+        report("moe_gemm (down)", case, us, used * f * W * 2.0 + pairs * (f * 2.0 + W * 4.0), 2.0 * pairs * f * W)
+        gm = GemmBf16.get()
+        rows_all = n_tok * top
+        a_all = torch.randn((rows_all, W), device=dev, dtype=bf)
+        c_all = torch.empty((rows_all, f), device=dev, dtype=bf)
+        if gm.run(a_all, w_up[0], c_all, ops.MODE_SWIGLU):
+            us = _time(lambda: gm.run(a_all, w_up[0], c_all, ops.MODE_SWIGLU), iters)
+            report("  like: gemm_tc (gate, up, act)", case, us, 2 * f * W * 2.0 + rows_all * (W + f) * 2.0,
+                   4.0 * rows_all * f * W)
+        us = _time(lambda: o.moe_combine(yk, row_of, wt, xn, x, accumulate=False), iters)
+        report("moe_combine", case, us, n_tok * W * (4.0 * top + 6.0), 0.0)
+    return rows
+
+
 def step(B: int, context: int, prefill: int, layers: int, iters: int) -> None:
     from . import from_random
     from .config import config_from_dict
@@ -478,14 +663,14 @@ def timeline(B: int, context: int, layers: int) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("what", choices=["gemm", "attn-decode", "attn-prefill", "elementwise", "step", "timeline", "decode",
-                                     "kikopel-kernels"])
+                                     "kikopel-kernels", "tovapel-kernels"])
     ap.add_argument("sizes", type=int, nargs="+")
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--layers", type=int, default=4, help="layers of the model that `step` builds")
     ap.add_argument("--model", default="mistral7b", choices=sorted(MODEL_SIZES),
                     help="step, timeline: whose layer sizes the model has")
     ap.add_argument("--kikopel-size", default="1b", choices=sorted(KIKOPEL_SIZES),
-                    help="kikopel-kernels TOKENS BATCH CONTEXT: whose layer sizes the kernels get")
+                    help="kikopel-kernels / tovapel-kernels TOKENS BATCH CONTEXT: whose layer sizes the kernels get")
     ap.add_argument("--window", type=int, default=0, help="decode: the sliding window (0: none)")
     ap.add_argument("--equal-shares", action="store_true",
                     help="decode: every sequence's keys in equal shares (no page quantum)")
@@ -497,6 +682,9 @@ def main() -> None:
     if a.splits:
         from .csrc import attention_bf16
         attention_bf16.decode_splits = lambda *args, **kw: a.splits
+    if a.what == "tovapel-kernels":
+        tovapel_kernels(a.kikopel_size, a.sizes[0], a.sizes[1], a.sizes[2], a.iters)
+        return
     if a.what == "kikopel-kernels":
         kikopel_kernels(a.kikopel_size, a.sizes[0], a.sizes[1], a.sizes[2], a.iters)
     elif a.what == "gemm":
