@@ -287,3 +287,175 @@ extern "C" int TL_NAME(tl_moe_combine)(const float* yk, const int* row_of, const
   return tl_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, yk, row_of, wt, (const act_t*)h, out, ldo,
                    H, top, accumulate);
 }
+
+#if TL_DTYPE == 1
+// ---------------------------------------------------------------------------
+// The same grouped products on tensor cores (bfloat16): a block takes 64 rows of one expert's group
+// and 64 output columns (the gate and the up columns of the same numbers together); operands come in
+// steps of 32 along K through shared memory with cp.async, three steps in flight; mma.sync m16n8k16
+// with fragments by ldmatrix from swizzled tiles, a warp per 16 rows.  A weight matrix [N][K] is the
+// B operand as it lies.  With few rows per expert (decode) the blocks mostly stream weights, which is
+// then the whole cost.
+// ---------------------------------------------------------------------------
+#define MBM 64
+#define MBN 64
+#define MBK 32
+#define MSTAGES 3
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void moe_cp_async16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void moe_ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void moe_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// rows of 32 elements are four 16-byte chunks; chunk c of row r lies at c ^ ((r >> 1) & 3)
+__device__ __forceinline__ int moe_swz(int row, int chunk) { return chunk ^ ((row >> 1) & 3); }
+
+template <bool UP>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__ row_token,
+                    const bf16* __restrict__ W, void* __restrict__ C, int ldc, const int* __restrict__ offsets,
+                    int E, int N, int K, float limit, float alpha) {
+  __shared__ __align__(128) bf16 As[MSTAGES][MBM * MBK];
+  __shared__ __align__(128) bf16 Ws[MSTAGES][MBN * MBK];
+  __shared__ __align__(128) bf16 Us[UP ? MSTAGES : 1][UP ? MBN * MBK : 8];
+  __shared__ int src_row[MBM];
+  __shared__ int tile_info[3];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    int tile = blockIdx.y, e = 0, found = -1;
+    for (; e < E; ++e) {
+      const int tiles = (offsets[e + 1] - offsets[e] + MBM - 1) / MBM;
+      if (tile < tiles) { found = e; break; }
+      tile -= tiles;
+    }
+    tile_info[0] = found;
+    if (found >= 0) {
+      tile_info[1] = offsets[found] + tile * MBM;
+      const int left = offsets[found + 1] - tile_info[1];
+      tile_info[2] = left < MBM ? left : MBM;
+    }
+  }
+  __syncthreads();
+  const int e = tile_info[0];
+  if (e < 0) return;
+  const int r0 = tile_info[1], rows = tile_info[2];
+  if (tid < MBM) src_row[tid] = tid < rows ? (UP ? row_token[r0 + tid] : r0 + tid) : -1;
+  __syncthreads();
+  const bf16* We = W + (size_t)e * (UP ? 2 : 1) * N * K;
+  const int n0 = blockIdx.x * MBN;
+  const int k_iters = (K + MBK - 1) / MBK;
+
+  auto load_stage = [&](int ki, int st) {
+    const int k0 = ki * MBK;
+    // 64 rows x 4 chunks per operand: two chunks per thread and operand
+    for (int i = tid; i < MBM * 4; i += 128) {
+      const int row = i >> 2, chunk = i & 3;
+      const int k = k0 + chunk * 8;
+      bf16* da = &As[st][row * MBK + moe_swz(row, chunk) * 8];
+      const int ar = src_row[row];
+      if (ar >= 0 && k < K) moe_cp_async16(da, A + (size_t)ar * lda + k);
+      else *reinterpret_cast<uint4*>(da) = make_uint4(0, 0, 0, 0);
+      bf16* dw = &Ws[st][row * MBK + moe_swz(row, chunk) * 8];
+      const int wn = n0 + row;
+      if (wn < N && k < K) moe_cp_async16(dw, We + (size_t)wn * K + k);
+      else *reinterpret_cast<uint4*>(dw) = make_uint4(0, 0, 0, 0);
+      if (UP) {
+        bf16* du = &Us[st][row * MBK + moe_swz(row, chunk) * 8];
+        if (wn < N && k < K) moe_cp_async16(du, We + (size_t)(N + wn) * K + k);
+        else *reinterpret_cast<uint4*>(du) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  float acc[MBN / 8][4], acu[UP ? MBN / 8 : 1][4];
+#pragma unroll
+  for (int n = 0; n < MBN / 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.0f;
+  if (UP) {
+#pragma unroll
+    for (int n = 0; n < MBN / 8; ++n) acu[n][0] = acu[n][1] = acu[n][2] = acu[n][3] = 0.0f;
+  }
+#pragma unroll
+  for (int s = 0; s < MSTAGES - 1; ++s) {
+    if (s < k_iters) load_stage(s, s);
+    asm volatile("cp.async.commit_group;");
+  }
+  for (int ki = 0; ki < k_iters; ++ki) {
+    const int st = ki % MSTAGES;
+    asm volatile("cp.async.wait_group %0;" ::"n"(MSTAGES - 2));
+    __syncthreads();                                     // stage ki is there, and stage ki - 1 is free
+    if (ki + MSTAGES - 1 < k_iters) load_stage(ki + MSTAGES - 1, (ki + MSTAGES - 1) % MSTAGES);
+    asm volatile("cp.async.commit_group;");
+#pragma unroll
+    for (int kk = 0; kk < MBK / 16; ++kk) {
+      unsigned af[4];
+      {
+        const int row = warp * 16 + (lane & 15), chunk = kk * 2 + (lane >> 4);
+        moe_ldmatrix_x4(af, &As[st][row * MBK + moe_swz(row, chunk) * 8]);
+      }
+#pragma unroll
+      for (int np = 0; np < MBN / 16; ++np) {
+        const int row = np * 16 + (lane >> 4) * 8 + (lane & 7), chunk = kk * 2 + ((lane >> 3) & 1);
+        unsigned bfr[4];
+        moe_ldmatrix_x4(bfr, &Ws[st][row * MBK + moe_swz(row, chunk) * 8]);
+        moe_mma(acc[2 * np], af, bfr[0], bfr[1]);
+        moe_mma(acc[2 * np + 1], af, bfr[2], bfr[3]);
+        if (UP) {
+          moe_ldmatrix_x4(bfr, &Us[st][row * MBK + moe_swz(row, chunk) * 8]);
+          moe_mma(acu[2 * np], af, bfr[0], bfr[1]);
+          moe_mma(acu[2 * np + 1], af, bfr[2], bfr[3]);
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;");
+  const int ra = warp * 16 + (lane >> 2), rb = ra + 8;
+#pragma unroll
+  for (int n = 0; n < MBN / 8; ++n) {
+    const int c = n0 + n * 8 + (lane & 3) * 2;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = half ? rb : ra;
+      if (m >= rows) continue;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        if (c + j >= N) continue;
+        const float v = acc[n][half * 2 + j];
+        if (UP) {
+          const float g = fminf(v, limit);
+          const float u = fminf(fmaxf(acu[n][half * 2 + j], -limit), limit);
+          ((bf16*)C)[(size_t)(r0 + m) * ldc + c + j] = __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+        } else {
+          ((float*)C)[(size_t)(r0 + m) * ldc + c + j] = v;
+        }
+      }
+    }
+  }
+}
+
+extern "C" int tl_moe_gemm_mma(const void* A, int lda, const int* row_token, const void* W, void* C, int ldc,
+                               const int* offsets, int E, int max_rows, int N, int K, int up, float limit,
+                               float alpha, cudaStream_t stream) {
+  if (max_rows <= 0 || E <= 0) return 0;
+  if (N < 1 || K < 1) return TL_ERR_BAD_ARG;
+  if (K % 8 || lda % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TL_ERR_UNSUPPORTED;
+  const int tiles = (max_rows + MBM - 1) / MBM + E;
+  if (tiles > 65535) return TL_ERR_UNSUPPORTED;
+  dim3 grid((N + MBN - 1) / MBN, tiles);
+  if (up)
+    return tl_launch(moe_gemm_mma_kernel<true>, grid, dim3(128), 0, stream, (const bf16*)A, lda, row_token,
+                     (const bf16*)W, C, ldc, offsets, E, N, K, limit, alpha);
+  return tl_launch(moe_gemm_mma_kernel<false>, grid, dim3(128), 0, stream, (const bf16*)A, lda, row_token,
+                   (const bf16*)W, C, ldc, offsets, E, N, K, limit, alpha);
+}
+#endif

@@ -6,7 +6,7 @@ a CUDA device, a missing library or a launch that the driver rejects raises
 """
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Callable, Dict, Optional
 
 import torch
@@ -135,7 +135,7 @@ class CoreOps:
                      "tl_gemm_generic", "tl_attn_generic", "tl_pair_embed_add", "tl_branch_norm_add", "tl_poly_norm",
                      "tl_latent_prep", "tl_headwise_gemm", "tl_latent_attn", "tl_gated_scan", "tl_gated_scan_groups",
                      "tl_stream_spread", "tl_stream_sum", "tl_hc_read_norm", "tl_hc_write", "tl_branch_norm_mean",
-                     "tl_headnorm_silu_gate", "tl_qk_norm_cache_write", "tl_sink_attn", "tl_gla_scan",
+                     "tl_headnorm_silu_gate", "tl_qk_norm_cache_write", "tl_sink_attn", "tl_gla_scan", "tl_gla_scan_scratch",
                      "tl_moe_route", "tl_moe_plan", "tl_moe_gemm", "tl_moe_combine"):
             fn = getattr(self.lib, f"{base}_{self.suffix}")
             fn.restype = c_int
@@ -644,10 +644,13 @@ class CoreOps:
     # ---- gated linear attention ---------------------------------------------------------------------
     def gla_scan(self, zq: torch.Tensor, zk: torch.Tensor, zv: torch.Tensor, za: torch.Tensor,
                  bias: Optional[torch.Tensor], tau: float, q_scale: float, state: torch.Tensor, out: torch.Tensor,
-                 seq_start: torch.Tensor, seq_slot: torch.Tensor, heads: int, dim: int, vdim: int) -> None:
+                 seq_start: torch.Tensor, seq_slot: torch.Tensor, heads: int, dim: int, vdim: int,
+                 workspace=None, chunked: bool = True) -> None:
         """S <- diag(alpha) S + k v^T, o = S^T (q * q_scale) over each sequence's tokens of the step, from and
         into `state` [slots, heads, dim, vdim]; alpha = sigmoid(za + bias)^(1 / tau).  zq, zk, zv are column
-        ranges of one 32-bit product (one row stride); `za` may be overwritten with the decays."""
+        ranges of one 32-bit product (one row stride); `za` may be overwritten with the decays.  Long steps
+        run in three passes over chunks of 64 tokens (`chunked`; the same sums in another order), with
+        scratch from `workspace`."""
         for t, n in ((zq, "q"), (zk, "k"), (zv, "v"), (za, "decay pre-activations")):
             _need(t, torch.float32, "recurrence " + n, contiguous=False)
             if t.stride(1) != 1:
@@ -661,13 +664,23 @@ class CoreOps:
             raise KernelError("gla_scan: sizes do not match")
         if bias is not None:
             _need(bias, torch.float32, "decay bias")
+        scratch = None
+        self._tl_gla_scan_scratch.restype = c_longlong
+        n = int(self._tl_gla_scan_scratch(c_int(T), c_int(seq_slot.numel()), c_int(heads), c_int(dim),
+                                          c_int(vdim))) if chunked else 0
+        if n:
+            scratch = (workspace.get("gla_chunks", (n,), torch.float32) if workspace is not None
+                       else torch.empty(n, dtype=torch.float32, device=zq.device))
         _check(self._tl_gla_scan(_ptr(zq), _ptr(zk), _ptr(zv), c_int(zq.stride(0)), _ptr(za), c_int(za.stride(0)),
                                  _ptr(bias), c_float(tau), c_float(q_scale), _ptr(state), _ptr(out),
                                  c_int(out.stride(0)), _ptr(seq_start), _ptr(seq_slot), c_int(T),
-                                 c_int(seq_slot.numel()), c_int(heads), c_int(dim), c_int(vdim), _stream()),
-               "gla_scan")
+                                 c_int(seq_slot.numel()), c_int(heads), c_int(dim), c_int(vdim), _ptr(scratch),
+                                 _stream()), "gla_scan")
         if T > 4 * seq_slot.numel():
             _check(0, "gla_decay")
+        if n:
+            _check(0, "gla_chunk_carry")
+            _check(0, "gla_chunk_apply")
 
     # ---- mixture of experts ---------------------------------------------------------------------------
     def moe_route(self, z: torch.Tensor, correction: Optional[torch.Tensor], top: int, idx: torch.Tensor,
@@ -708,6 +721,15 @@ class CoreOps:
         N = rows_w // 2 if up else rows_w
         if a.shape[1] != K or c.shape[1] != N or offsets.numel() != E + 1 or (up and row_token is None):
             raise KernelError("moe_gemm: sizes do not match")
+        if self.act_dtype == torch.bfloat16:
+            # the tensor-core kernel, where alignments allow it
+            self.lib.tl_moe_gemm_mma.restype = c_int
+            st = self.lib.tl_moe_gemm_mma(_ptr(a), c_int(a.stride(0)), _ptr(row_token), _ptr(w), _ptr(c),
+                                          c_int(c.stride(0)), _ptr(offsets), c_int(E), c_int(c.shape[0]), c_int(N),
+                                          c_int(K), c_int(1 if up else 0), c_float(limit), c_float(alpha), _stream())
+            if st != -2:
+                _check(st, "moe_gemm_mma")
+                return
         _check(self._tl_moe_gemm(_ptr(a), c_int(a.stride(0)), _ptr(row_token), _ptr(w), _ptr(c), c_int(c.stride(0)),
                                  _ptr(offsets), c_int(E), c_int(c.shape[0]), c_int(N), c_int(K), c_int(1 if up else 0),
                                  c_float(limit), c_float(alpha), _stream()), "moe_gemm")

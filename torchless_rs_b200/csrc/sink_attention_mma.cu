@@ -2,8 +2,8 @@
 // (what it computes: sink_attention.cu), for one pair of key and value sizes per library
 // (-DSA_DIM, -DSA_VDIM, multiples of 16 up to 128).
 //
-//   sink_attn_mma_kernel     steps of many tokens: a block takes 64 consecutive tokens of one sequence
-//                            and one query head; keys and values come page by page (64 keys) into
+//   sink_attn_mma_kernel     steps of many tokens: a block takes 128 consecutive tokens of one sequence
+//                            and one query head, a warp 16 of them; keys and values come page by page (64 keys) into
 //                            shared memory with cp.async, two pages in flight; Q K^T and P V on the
 //                            tensor cores (mma.sync m16n8k16, fragments by ldmatrix from swizzled
 //                            tiles: a key page is the B operand as it lies, and so is the transposed
@@ -30,7 +30,7 @@
 #endif
 
 constexpr int DIM = SA_DIM, VDIM = SA_VDIM;
-constexpr int BM = 64, BN = TL_PAGE, THREADS = 128;
+constexpr int BM = 128, BN = TL_PAGE, THREADS = 128, MMA_THREADS = 256;
 static_assert(TL_PAGE == 64, "a page is one key tile of 64");
 static_assert(DIM % 16 == 0 && VDIM % 16 == 0 && DIM >= 16 && VDIM >= 16 && DIM <= 128 && VDIM <= 128, "sizes");
 #define LOG2E 1.4426950408889634f
@@ -70,17 +70,19 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
 }
-// tanh through one exponential: 1 - 2 / (e^(2x) + 1); exact limits at both ends
+// The hardware's tanh (relative error 2^-11): a capped score is off by at most that fraction of
+// itself, an eighth of what the rounding of q and k to bfloat16 already does to it.
 __device__ __forceinline__ float tanh_fast(float x) {
-  const float e = __expf(2.0f * x);
-  return 1.0f - __fdividef(2.0f, e + 1.0f);
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 // A tile's rows of R elements, contiguous in global memory, into a swizzled shared tile.
 template <int R, int ROWS>
 __device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, int tid) {
   constexpr int C = R / 8;
-  for (int i = tid; i < ROWS * C; i += THREADS) {
+  for (int i = tid; i < ROWS * C; i += MMA_THREADS) {
     const int row = i / C, chunk = i - row * C;
     cp_async16(dst + row * R + swz<R>(row, chunk) * 8, src + (size_t)i * 8);
   }
@@ -104,7 +106,7 @@ __device__ __forceinline__ TilePages tile_pages(int p_first, int p_last, int win
   return t;
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(MMA_THREADS)
 sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                      const float* __restrict__ gate, int ldg, const float* __restrict__ sink,
                      bf16* __restrict__ out, const int* __restrict__ token_pos, const int* __restrict__ seq_start,
@@ -145,7 +147,7 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
   // Q tile (rows beyond the sequence's end are zero) and the first page
   {
     constexpr int C = DIM / 8;
-    for (int i = tid; i < BM * C; i += THREADS) {
+    for (int i = tid; i < BM * C; i += MMA_THREADS) {
       const int row = i / C, chunk = i - row * C;
       bf16* dst = Qs + row * DIM + swz<DIM>(row, chunk) * 8;
       if (row < rows) cp_async16(dst, q + ((size_t)(t0 + row) * nh + h) * DIM + chunk * 8);
@@ -171,6 +173,9 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
   unsigned qf[DIM / 16][4];
   const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
   const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
+  // what this warp's 16 rows span; a warp without rows only helps to load
+  const int wrows = rows - warp * 16;
+  const int wp_first = p_first + warp * 16, wp_last = wp_first + (wrows < 16 ? wrows : 16) - 1;
 
   for (int it = 0; it < tp.n_iter; ++it) {
     const int buf = it & 1;
@@ -188,6 +193,13 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
     const bf16* Kb = Ks + buf * BN * DIM;
     const bf16* Vb = Vs + buf * VDIM * BN;
     const int key0 = tp.col(it) * TL_PAGE;
+    // a page that none of the warp's rows sees (keys after its last row, or before its first row's window
+    // and not kept) is passed over; a page that all of them see whole needs no mask
+    const bool none = wrows <= 0 || key0 > wp_last ||
+                      (window > 0 && wp_first - (key0 + BN - 1) >= window && key0 >= keep_first);
+    if (none) { __syncthreads(); continue; }
+    const bool whole = wrows >= 16 && key0 + BN - 1 <= wp_first &&
+                       (window <= 0 || wp_last - key0 < window || key0 + BN - 1 < keep_first);
     // S = Q K^T : 16 rows x 64 keys per warp
     float s[BN / 8][4];
 #pragma unroll
@@ -212,7 +224,7 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
         const int j = key0 + n * 8 + (lane & 3) * 2 + (e & 1);
         const int i = e < 2 ? pos0 : pos1;
         float v = cap > 0.0f ? cap2 * tanh_fast(s[n][e] * scale * inv_cap) : s[n][e] * scale2;
-        const bool vis = j <= i && (window <= 0 || i - j < window || j < keep_first);
+        const bool vis = whole || (j <= i && (window <= 0 || i - j < window || j < keep_first));
         v = vis ? v : -INFINITY;
         s[n][e] = v;
         if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
@@ -290,7 +302,7 @@ extern "C" int tl_sink_attn_mma(const void* q, const void* k_pages, const void* 
     set = true;
   }
   const int tiles = (T + BM - 1) / BM + n_seqs;      // an upper bound; a block without a tile leaves
-  return tl_launch(sink_attn_mma_kernel, dim3(tiles, nh), dim3(THREADS), smem, stream, (const bf16*)q,
+  return tl_launch(sink_attn_mma_kernel, dim3(tiles, nh), dim3(MMA_THREADS), smem, stream, (const bf16*)q,
                    (const bf16*)k_pages, (const bf16*)v_pages, gate, ldg, sink, (bf16*)out, token_pos, seq_start,
                    seq_slot, page_table, table_stride, n_seqs, nh, nkv, window, keep_first, scale, cap);
 }

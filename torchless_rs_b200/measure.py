@@ -431,7 +431,7 @@ def tovapel_kernels(size: str, T: int, B: int, ctx: int, iters: int, file=None) 
         ab = torch.zeros(rh * rd, device=dev)
         hd, hv = rh * rd, rh * rv
         us = _time(lambda: o.gla_scan(zz[:, :hd], zz[:, hd:2 * hd], zz[:, 2 * hd:2 * hd + hv], za, ab, 16.0, 0.125,
-                                      state, so, start, slot, rh, rd, rv), few)
+                                      state, so, start, slot, rh, rd, rv, workspace=ws), few)
         scan_b = n_tok * (3 * hd + 2 * hv) * 4.0 + seqs * hd * rv * 8.0
         report("gla_scan", case, us, scan_b, 4.0 * n_tok * hd * rv)
         z2 = torch.randn((n_tok, 2 * hd + hv), device=dev)

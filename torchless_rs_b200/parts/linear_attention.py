@@ -95,7 +95,7 @@ class GatedLinearAttention:
         self.matmul(low, self.w_a2, za, ops.MODE_STORE_F32)
         o = ws.get("gla_out", (T, hv), torch.float32)
         rt.ops.gla_scan(z[:, :hd], z[:, hd:2 * hd], z[:, 2 * hd:2 * hd + hv], za, self.a_bias, self.tau,
-                        dim ** -0.5, self.state, o, batch.seq_start, batch.seq_slot, H, dim, vdim)
+                        dim ** -0.5, self.state, o, batch.seq_start, batch.seq_slot, H, dim, vdim, workspace=ws)
         gated = ws.get("gla_gated", (T, hv), rt.act_dtype)
         rt.ops.headnorm_silu_gate(o, self.norm_w, self.eps, z[:, 2 * hd + hv:], gated, H, vdim)
         self.matmul(gated, self.w_o, residual, ops.MODE_STORE_F32 if overwrite else ops.MODE_ACCUM_F32)
