@@ -58,7 +58,7 @@ extern "C" int TL_NAME(tl_stream_sum)(const float* xs, const int* rows, float* x
 __global__ void __launch_bounds__(256)
 hc_read_norm_kernel(const float* __restrict__ xs, const float* __restrict__ a, const float* __restrict__ w,
                     float eps, act_t* __restrict__ out, int H, int S) {
-  extern __shared__ float u_s[];
+  extern __shared__ __align__(16) float u_s[];
   __shared__ float scratch[33];
   __shared__ float a_s[HC_MAX_STREAMS];
   pdl_wait();
@@ -68,11 +68,26 @@ hc_read_norm_kernel(const float* __restrict__ xs, const float* __restrict__ a, c
   const int t = blockIdx.x;
   const float* src = xs + (size_t)t * S * H;
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float u = a_s[0] * src[i];
-    for (int s = 1; s < S; ++s) u = fmaf(a_s[s], src[(size_t)s * H + i], u);
-    u_s[i] = u;
-    ss = fmaf(u, u, ss);
+  if ((H & 3) == 0) {
+    // 16 bytes per load (rows of the streams start on 16-byte boundaries when H is a multiple of 4)
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 u = *reinterpret_cast<const float4*>(src + i);
+      u.x *= a_s[0]; u.y *= a_s[0]; u.z *= a_s[0]; u.w *= a_s[0];
+      for (int s = 1; s < S; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(src + (size_t)s * H + i);
+        u.x = fmaf(a_s[s], v.x, u.x); u.y = fmaf(a_s[s], v.y, u.y);
+        u.z = fmaf(a_s[s], v.z, u.z); u.w = fmaf(a_s[s], v.w, u.w);
+      }
+      *reinterpret_cast<float4*>(u_s + i) = u;
+      ss = fmaf(u.x, u.x, fmaf(u.y, u.y, fmaf(u.z, u.z, fmaf(u.w, u.w, ss))));
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float u = a_s[0] * src[i];
+      for (int s = 1; s < S; ++s) u = fmaf(a_s[s], src[(size_t)s * H + i], u);
+      u_s[i] = u;
+      ss = fmaf(u, u, ss);
+    }
   }
   const float total = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(total / (float)H + eps);
@@ -98,7 +113,7 @@ __global__ void __launch_bounds__(256)
 hc_write_kernel(float* __restrict__ xs, const float* __restrict__ M, const float* __restrict__ b,
                 const float* __restrict__ y, int ldy, int H, int S, const float* __restrict__ a2,
                 const float* __restrict__ w2, float eps2, act_t* __restrict__ out2) {
-  extern __shared__ float u_s[];
+  extern __shared__ __align__(16) float u_s[];
   __shared__ float scratch[33];
   __shared__ float m_s[HC_MAX_STREAMS * HC_MAX_STREAMS], b_s[HC_MAX_STREAMS], a_s[HC_MAX_STREAMS];
   pdl_wait();
@@ -113,6 +128,43 @@ hc_write_kernel(float* __restrict__ xs, const float* __restrict__ M, const float
   float* row = xs + (size_t)t * S * H;
   const float* yr = y + (size_t)t * ldy;
   float ss = 0.0f;
+  if ((H & 3) == 0 && (ldy & 3) == 0 && S <= 4) {
+    // four coordinates per thread, 16 bytes per load and store (the usual case of up to four streams)
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 old[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s)
+        old[s] = s < S ? *reinterpret_cast<const float4*>(row + (size_t)s * H + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 yv = *reinterpret_cast<const float4*>(yr + i);
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j < S) {
+          float4 v;
+          v.x = m_s[j] * old[0].x; v.y = m_s[j] * old[0].y; v.z = m_s[j] * old[0].z; v.w = m_s[j] * old[0].w;
+#pragma unroll
+          for (int s = 1; s < 4; ++s)
+            if (s < S) {
+              const float m = m_s[s * S + j];
+              v.x = fmaf(m, old[s].x, v.x); v.y = fmaf(m, old[s].y, v.y);
+              v.z = fmaf(m, old[s].z, v.z); v.w = fmaf(m, old[s].w, v.w);
+            }
+          v.x = fmaf(b_s[j], yv.x, v.x); v.y = fmaf(b_s[j], yv.y, v.y);
+          v.z = fmaf(b_s[j], yv.z, v.z); v.w = fmaf(b_s[j], yv.w, v.w);
+          *reinterpret_cast<float4*>(row + (size_t)j * H + i) = v;
+          if (j == 0) { u.x = a_s[0] * v.x; u.y = a_s[0] * v.y; u.z = a_s[0] * v.z; u.w = a_s[0] * v.w; }
+          else {
+            u.x = fmaf(a_s[j], v.x, u.x); u.y = fmaf(a_s[j], v.y, u.y);
+            u.z = fmaf(a_s[j], v.z, u.z); u.w = fmaf(a_s[j], v.w, u.w);
+          }
+        }
+      }
+      if (a2 != nullptr) {
+        *reinterpret_cast<float4*>(u_s + i) = u;
+        ss = fmaf(u.x, u.x, fmaf(u.y, u.y, fmaf(u.z, u.z, fmaf(u.w, u.w, ss))));
+      }
+    }
+  } else
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float old[HC_MAX_STREAMS];
 #pragma unroll
@@ -172,14 +224,37 @@ branch_norm_mean_kernel(BranchPtrs p, int n, int H, float eps, float* __restrict
   pdl_launch_dependents();
   const int t = blockIdx.x;
   float inv[BR_MAX];
+  const bool vec = (H & 3) == 0;
   for (int b = 0; b < n; ++b) {
     const float* y = p.y[b] + (size_t)t * H;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) ss = fmaf(y[i], y[i], ss);
+    if (vec) {
+      for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(y + i);
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+      }
+    } else {
+      for (int i = threadIdx.x; i < H; i += blockDim.x) ss = fmaf(y[i], y[i], ss);
+    }
     const float total = block_sum(ss, scratch);
     inv[b] = 1.0f / sqrtf(total / (float)H + eps);
   }
   const float share = 1.0f / (float)n;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int b = 0; b < n; ++b) {
+        const float4 v = *reinterpret_cast<const float4*>(p.y[b] + (size_t)t * H + i);
+        const float4 w = *reinterpret_cast<const float4*>(p.w[b] + i);
+        a.x += v.x * inv[b] * w.x; a.y += v.y * inv[b] * w.y; a.z += v.z * inv[b] * w.z; a.w += v.w * inv[b] * w.w;
+      }
+      a.x *= share; a.y *= share; a.z *= share; a.w *= share;
+      float4* o = reinterpret_cast<float4*>(out + (size_t)t * H + i);
+      if (accumulate) { const float4 c = *o; a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w; }
+      *o = a;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float a = 0.0f;
     for (int b = 0; b < n; ++b) a += p.y[b][(size_t)t * H + i] * inv[b] * p.w[b][i];
