@@ -11,6 +11,14 @@
 
 #define HC_MAX_STREAMS 8
 
+// Threads of a row kernel: one per four coordinates (a row is then one round of 16-byte loads, all in
+// flight at once), between 128 and 1024.
+static inline int row_threads(int H) {
+  int t = ((H + 3) / 4 + 31) / 32 * 32;
+  return t < 128 ? 128 : (t > 1024 ? 1024 : t);
+}
+
+
 // xs[t, s, :] = x[t, :] for every s.
 __global__ void stream_spread_kernel(const float* __restrict__ x, float* __restrict__ xs, int H, int S) {
   pdl_wait();
@@ -38,6 +46,17 @@ __global__ void stream_sum_kernel(const float* __restrict__ xs, const int* __res
   const int r = blockIdx.x;
   const int t = rows != nullptr ? rows[r] : r;
   const float* src = xs + (size_t)t * S * H;
+  if ((H & 3) == 0) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 a = *reinterpret_cast<const float4*>(src + i);
+      for (int s = 1; s < S; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(src + (size_t)s * H + i);
+        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+      }
+      *reinterpret_cast<float4*>(x + (size_t)r * H + i) = a;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float a = src[i];
     for (int s = 1; s < S; ++s) a += src[(size_t)s * H + i];
@@ -49,13 +68,13 @@ extern "C" int TL_NAME(tl_stream_sum)(const float* xs, const int* rows, float* x
                                       cudaStream_t stream) {
   if (R <= 0) return 0;
   if (S < 1 || H < 1) return TL_ERR_BAD_ARG;
-  return tl_launch(stream_sum_kernel, dim3(R), dim3(256), 0, stream, xs, rows, x, H, S);
+  return tl_launch(stream_sum_kernel, dim3(R), dim3(row_threads(H)), 0, stream, xs, rows, x, H, S);
 }
 
 // out[t, :] = act( u / sqrt(mean(u^2) + eps) * w ),  u = sum_s a[s] xs[t, s, :].
 // `w` is the 32-bit factor per coordinate (a norm whose stored weight lies around zero hands in
 // 1 + weight).  u is kept in shared memory between the two passes (H floats).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 hc_read_norm_kernel(const float* __restrict__ xs, const float* __restrict__ a, const float* __restrict__ w,
                     float eps, act_t* __restrict__ out, int H, int S) {
   extern __shared__ __align__(16) float u_s[];
@@ -103,13 +122,13 @@ extern "C" int TL_NAME(tl_hc_read_norm)(const float* xs, const float* a, const f
   if (smem > 200 * 1024) return TL_ERR_UNSUPPORTED;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(hc_read_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return tl_launch(hc_read_norm_kernel, dim3(T), dim3(256), smem, stream, xs, a, w, eps, (act_t*)out, H, S);
+  return tl_launch(hc_read_norm_kernel, dim3(T), dim3(row_threads(H)), smem, stream, xs, a, w, eps, (act_t*)out, H, S);
 }
 
 // xs'[t, j, :] = sum_s M[s, j] xs[t, s, :] + b[j] y[t, :], in place (a coordinate's S values are
 // read before any is written).  With `a2` given the kernel goes on to the next sublayer's read:
 // out2[t, :] = act( u2 / rms(u2) * w2 ) with u2 = sum_j a2[j] xs'[t, j, :].
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 hc_write_kernel(float* __restrict__ xs, const float* __restrict__ M, const float* __restrict__ b,
                 const float* __restrict__ y, int ldy, int H, int S, const float* __restrict__ a2,
                 const float* __restrict__ w2, float eps2, act_t* __restrict__ out2) {
@@ -205,7 +224,7 @@ extern "C" int TL_NAME(tl_hc_write)(float* xs, const float* M, const float* b, c
   if (smem > 200 * 1024) return TL_ERR_UNSUPPORTED;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(hc_write_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return tl_launch(hc_write_kernel, dim3(T), dim3(256), smem, stream, xs, M, b, y, ldy, H, S, a2, w2, eps2,
+  return tl_launch(hc_write_kernel, dim3(T), dim3(row_threads(H)), smem, stream, xs, M, b, y, ldy, H, S, a2, w2, eps2,
                    (act_t*)out2);
 }
 
@@ -217,7 +236,7 @@ struct BranchPtrs {
   const float* w[BR_MAX];
 };
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 branch_norm_mean_kernel(BranchPtrs p, int n, int H, float eps, float* __restrict__ out, int accumulate) {
   __shared__ float scratch[33];
   pdl_wait();
@@ -225,6 +244,38 @@ branch_norm_mean_kernel(BranchPtrs p, int n, int H, float eps, float* __restrict
   const int t = blockIdx.x;
   float inv[BR_MAX];
   const bool vec = (H & 3) == 0;
+  const float share0 = 1.0f / (float)n;
+  if (vec && H <= 4 * (int)blockDim.x) {
+    // a row is one round of loads: every branch's four values stay in registers between the sum of
+    // squares and the scaling, so the outputs are read once
+    const int i = threadIdx.x * 4;
+    float4 v[BR_MAX];
+#pragma unroll
+    for (int b = 0; b < BR_MAX; ++b) {
+      v[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (b < n && i < H) v[b] = *reinterpret_cast<const float4*>(p.y[b] + (size_t)t * H + i);
+    }
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int b = 0; b < BR_MAX; ++b) {
+      if (b < n) {
+        const float ss = fmaf(v[b].x, v[b].x, fmaf(v[b].y, v[b].y, fmaf(v[b].z, v[b].z, v[b].w * v[b].w)));
+        const float total = block_sum(ss, scratch);
+        const float r = 1.0f / sqrtf(total / (float)H + eps);
+        if (i < H) {
+          const float4 w = *reinterpret_cast<const float4*>(p.w[b] + i);
+          a.x += v[b].x * r * w.x; a.y += v[b].y * r * w.y; a.z += v[b].z * r * w.z; a.w += v[b].w * r * w.w;
+        }
+      }
+    }
+    if (i < H) {
+      a.x *= share0; a.y *= share0; a.z *= share0; a.w *= share0;
+      float4* o = reinterpret_cast<float4*>(out + (size_t)t * H + i);
+      if (accumulate) { const float4 c = *o; a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w; }
+      *o = a;
+    }
+    return;
+  }
   for (int b = 0; b < n; ++b) {
     const float* y = p.y[b] + (size_t)t * H;
     float ss = 0.0f;
@@ -273,7 +324,7 @@ extern "C" int TL_NAME(tl_branch_norm_mean)(const float* const* ys, const float*
     p.y[b] = ys[b];
     p.w[b] = ws[b];
   }
-  return tl_launch(branch_norm_mean_kernel, dim3(T), dim3(256), 0, stream, p, n, H, eps, out, accumulate);
+  return tl_launch(branch_norm_mean_kernel, dim3(T), dim3(row_threads(H)), 0, stream, p, n, H, eps, out, accumulate);
 }
 
 // Per-head output norm with a gate: out[t, h, :] = act( o[t, h, :] / rms * w[:] * silu(g[t, h, :]) ),

@@ -262,12 +262,34 @@ extern "C" int TL_NAME(tl_moe_gemm)(const void* A, int lda, const int* row_token
 }
 
 // out[t, :] (+)= sum_k wt[t, k] * ( row_of[t, k] >= 0 ? yk[row_of[t, k], :] : h[t, :] ), k in order.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 moe_combine_kernel(const float* __restrict__ yk, const int* __restrict__ row_of, const float* __restrict__ wt,
                    const act_t* __restrict__ h, float* __restrict__ out, int ldo, int H, int top, int accumulate) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
+  if ((H & 3) == 0 && (ldo & 3) == 0) {
+    // four coordinates per thread: a token's rows are one round of 16-byte loads
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < top; ++k) {
+        const int row = row_of[(size_t)t * top + k];
+        const float w = wt[(size_t)t * top + k];
+        float4 v;
+        if (row >= 0) {
+          v = *reinterpret_cast<const float4*>(yk + (size_t)row * H + i);
+        } else {
+          const act_t* hp = h + (size_t)t * H + i;
+          v = make_float4(to_f32(hp[0]), to_f32(hp[1]), to_f32(hp[2]), to_f32(hp[3]));
+        }
+        a.x = fmaf(w, v.x, a.x); a.y = fmaf(w, v.y, a.y); a.z = fmaf(w, v.z, a.z); a.w = fmaf(w, v.w, a.w);
+      }
+      float4* o = reinterpret_cast<float4*>(out + (size_t)t * ldo + i);
+      if (accumulate) { const float4 c = *o; a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w; }
+      *o = a;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float a = 0.0f;
     for (int k = 0; k < top; ++k) {
@@ -284,7 +306,9 @@ extern "C" int TL_NAME(tl_moe_combine)(const float* yk, const int* row_of, const
                                        float* out, int ldo, int T, int H, int top, int accumulate,
                                        cudaStream_t stream) {
   if (T <= 0) return 0;
-  return tl_launch(moe_combine_kernel, dim3(T), dim3(256), 0, stream, yk, row_of, wt, (const act_t*)h, out, ldo,
+  int threads = ((H + 3) / 4 + 31) / 32 * 32;
+  threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
+  return tl_launch(moe_combine_kernel, dim3(T), dim3(threads), 0, stream, yk, row_of, wt, (const act_t*)h, out, ldo,
                    H, top, accumulate);
 }
 

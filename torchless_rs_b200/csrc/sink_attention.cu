@@ -36,7 +36,8 @@ qk_norm_cache_write_kernel(const float* __restrict__ z, int ldz, const float* __
   const int in_page = pos % TL_PAGE;
   const float* row = z + (size_t)t * ldz;
   const int k_off = nh * dim, v_off = (nh + nkv) * dim;
-  for (int head = warp; head < nh + 2 * nkv; head += nwarps) {
+  // a warp per head; the heads of a token are spread over the blocks of a grid row
+  for (int head = blockIdx.y * nwarps + warp; head < nh + 2 * nkv; head += gridDim.y * nwarps) {
     if (head < nh + nkv) {
       const bool is_q = head < nh;
       const int off = head * dim;                      // q heads, then k heads
@@ -72,7 +73,12 @@ extern "C" int TL_NAME(tl_qk_norm_cache_write)(const float* z, int ldz, const fl
                                                int T, int nh, int nkv, int dim, int vdim, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (nh < 1 || nkv < 1 || dim < 1 || vdim < 1) return TL_ERR_BAD_ARG;
-  return tl_launch(qk_norm_cache_write_kernel, dim3(T), dim3(256), 0, stream, z, ldz, bias, qw, kw, eps,
+  // few tokens: a block of four warps per four heads, so that a token's heads are worked on at once; many
+  // tokens: a block per token
+  const int heads = nh + 2 * nkv;
+  const bool few = T < 512;
+  const dim3 grid(T, few ? (heads + 3) / 4 : 1);
+  return tl_launch(qk_norm_cache_write_kernel, grid, dim3(few ? 128 : 256), 0, stream, z, ldz, bias, qw, kw, eps,
                    (act_t*)q_out, (act_t*)k_pages, (act_t*)v_pages, token_pos, token_seq, seq_slot, page_table,
                    table_stride, nh, nkv, dim, vdim);
 }

@@ -13,7 +13,7 @@ from . import build
 from .ops import _check, _ptr, _sm_count, _stream
 
 MAX_SIZE = 128          # key and value sizes: multiples of 16 up to this
-MAX_GROUP = 8           # query heads per key/value head in the kernel for steps of few tokens
+MAX_GROUP = 16          # query heads per key/value head in the kernel for steps of few tokens
 FEW_TOKENS = 8          # a step whose sequences bring at most this many tokens each takes that kernel
 COMMON_SIZES = ((64, 64), (128, 128))     # built by the build check; others are built at first use
 

@@ -11,9 +11,10 @@
 //                            registers; the sink opens maximum and sum; the gate and 1/sum close.
 //   sink_attn_split_kernel   steps of few tokens (decode): a block takes one token, one key/value head
 //                            and a share of its pages, all query heads of the group at once (the
-//                            pages are read once for the group); 8 lanes per key for the scores, a
-//                            thread per value entry for the weighted sum; partial maximum, sum and
-//                            output go to a buffer,
+//                            pages are read once for the group); pages come into shared memory with
+//                            cp.async, the next one while this one is worked on; the tensor-core
+//                            tile's 16 rows are the group's heads, each warp takes 16 of the page's
+//                            keys; partial maximum, sum and output go to a buffer,
 //   sink_attn_merge_kernel   which joins the shares, counts the sink once and applies the gate.
 //
 // The pages a query tile needs: those of the kept first keys that lie before the window's first
@@ -79,10 +80,10 @@ __device__ __forceinline__ float tanh_fast(float x) {
 }
 
 // A tile's rows of R elements, contiguous in global memory, into a swizzled shared tile.
-template <int R, int ROWS>
+template <int R, int ROWS, int NT = MMA_THREADS>
 __device__ __forceinline__ void load_tile_async(bf16* dst, const bf16* src, int tid) {
   constexpr int C = R / 8;
-  for (int i = tid; i < ROWS * C; i += MMA_THREADS) {
+  for (int i = tid; i < ROWS * C; i += NT) {
     const int row = i / C, chunk = i - row * C;
     cp_async16(dst + row * R + swz<R>(row, chunk) * 8, src + (size_t)i * 8);
   }
@@ -106,7 +107,7 @@ __device__ __forceinline__ TilePages tile_pages(int p_first, int p_last, int win
   return t;
 }
 
-__global__ void __launch_bounds__(MMA_THREADS)
+__global__ void __launch_bounds__(MMA_THREADS, 2)
 sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                      const float* __restrict__ gate, int ldg, const float* __restrict__ sink,
                      bf16* __restrict__ out, const int* __restrict__ token_pos, const int* __restrict__ seq_start,
@@ -170,7 +171,6 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
   float o[VDIM / 8][4];
 #pragma unroll
   for (int n = 0; n < VDIM / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
-  unsigned qf[DIM / 16][4];
   const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
   const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
   // what this warp's 16 rows span; a warp without rows only helps to load
@@ -183,13 +183,6 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    if (it == 0) {
-#pragma unroll
-      for (int kk = 0; kk < DIM / 16; ++kk) {
-        const int row = warp * 16 + (lane & 15), chunk = kk * 2 + (lane >> 4);
-        ldmatrix_x4(qf[kk], Qs + row * DIM + swz<DIM>(row, chunk) * 8);
-      }
-    }
     const bf16* Kb = Ks + buf * BN * DIM;
     const bf16* Vb = Vs + buf * VDIM * BN;
     const int key0 = tp.col(it) * TL_PAGE;
@@ -200,75 +193,85 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
     if (none) { __syncthreads(); continue; }
     const bool whole = wrows >= 16 && key0 + BN - 1 <= wp_first &&
                        (window <= 0 || wp_last - key0 < window || key0 + BN - 1 < keep_first);
-    // S = Q K^T : 16 rows x 64 keys per warp
-    float s[BN / 8][4];
+    // the page in two halves of 32 keys, each with its own step of the running maximum and sum: half as
+    // many score registers, so that two blocks fit an SM
 #pragma unroll
-    for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+    for (int half = 0; half < 2; ++half) {
+      constexpr int HN = BN / 2;                 // keys per half
+      // S = Q K^T : 16 rows x 32 keys per warp
+      float s[HN / 8][4];
 #pragma unroll
-    for (int kk = 0; kk < DIM / 16; ++kk) {
+      for (int n = 0; n < HN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
 #pragma unroll
-      for (int np = 0; np < BN / 16; ++np) {
-        unsigned bfr[4];
-        const int row = np * 16 + (lane >> 4) * 8 + (lane & 7), chunk = kk * 2 + ((lane >> 3) & 1);
-        ldmatrix_x4(bfr, Kb + row * DIM + swz<DIM>(row, chunk) * 8);
-        mma_bf16(s[2 * np], qf[kk], bfr[0], bfr[1]);
-        mma_bf16(s[2 * np + 1], qf[kk], bfr[2], bfr[3]);
+      for (int kk = 0; kk < DIM / 16; ++kk) {
+        unsigned qa[4];
+        {
+          const int row = warp * 16 + (lane & 15), chunk = kk * 2 + (lane >> 4);
+          ldmatrix_x4(qa, Qs + row * DIM + swz<DIM>(row, chunk) * 8);
+        }
+#pragma unroll
+        for (int np = 0; np < HN / 16; ++np) {
+          unsigned bfr[4];
+          const int row = half * HN + np * 16 + (lane >> 4) * 8 + (lane & 7), chunk = kk * 2 + ((lane >> 3) & 1);
+          ldmatrix_x4(bfr, Kb + row * DIM + swz<DIM>(row, chunk) * 8);
+          mma_bf16(s[2 * np], qa, bfr[0], bfr[1]);
+          mma_bf16(s[2 * np + 1], qa, bfr[2], bfr[3]);
+        }
       }
-    }
-    // scale, cap, mask; the page's row maxima
-    float mx0 = -INFINITY, mx1 = -INFINITY;
+      float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int n = 0; n < BN / 8; ++n) {
+      for (int n = 0; n < HN / 8; ++n) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = key0 + n * 8 + (lane & 3) * 2 + (e & 1);
-        const int i = e < 2 ? pos0 : pos1;
-        float v = cap > 0.0f ? cap2 * tanh_fast(s[n][e] * scale * inv_cap) : s[n][e] * scale2;
-        const bool vis = whole || (j <= i && (window <= 0 || i - j < window || j < keep_first));
-        v = vis ? v : -INFINITY;
-        s[n][e] = v;
-        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        for (int e = 0; e < 4; ++e) {
+          const int j = key0 + half * HN + n * 8 + (lane & 3) * 2 + (e & 1);
+          const int i = e < 2 ? pos0 : pos1;
+          float v = cap > 0.0f ? cap2 * tanh_fast(s[n][e] * scale * inv_cap) : s[n][e] * scale2;
+          const bool vis = whole || (j <= i && (window <= 0 || i - j < window || j < keep_first));
+          v = vis ? v : -INFINITY;
+          s[n][e] = v;
+          if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        }
       }
-    }
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-    // (a row that has seen nothing yet and has no sink keeps -inf: its factors are taken as zero)
-    const float a0 = n0 == -INFINITY ? 0.0f : exp2f(m0 - n0), a1 = n1 == -INFINITY ? 0.0f : exp2f(m1 - n1);
-    const float b0 = n0 == -INFINITY ? 0.0f : n0, b1 = n1 == -INFINITY ? 0.0f : n1;
-    float sum0 = 0.0f, sum1 = 0.0f;
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      // (a row that has seen nothing yet and has no sink keeps -inf: its factors are taken as zero)
+      const float a0 = n0 == -INFINITY ? 0.0f : exp2f(m0 - n0), a1 = n1 == -INFINITY ? 0.0f : exp2f(m1 - n1);
+      const float b0 = n0 == -INFINITY ? 0.0f : n0, b1 = n1 == -INFINITY ? 0.0f : n1;
+      float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-    for (int n = 0; n < BN / 8; ++n) {
-      s[n][0] = exp2f(s[n][0] - b0); s[n][1] = exp2f(s[n][1] - b0);
-      s[n][2] = exp2f(s[n][2] - b1); s[n][3] = exp2f(s[n][3] - b1);
-      sum0 += s[n][0] + s[n][1];
-      sum1 += s[n][2] + s[n][3];
-    }
-    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
-    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
-    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
-    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
-    l0 = l0 * a0 + sum0; l1 = l1 * a1 + sum1;
-    m0 = n0; m1 = n1;
+      for (int n = 0; n < HN / 8; ++n) {
+        s[n][0] = exp2f(s[n][0] - b0); s[n][1] = exp2f(s[n][1] - b0);
+        s[n][2] = exp2f(s[n][2] - b1); s[n][3] = exp2f(s[n][3] - b1);
+        sum0 += s[n][0] + s[n][1];
+        sum1 += s[n][2] + s[n][3];
+      }
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+      l0 = l0 * a0 + sum0; l1 = l1 * a1 + sum1;
+      m0 = n0; m1 = n1;
 #pragma unroll
-    for (int n = 0; n < VDIM / 8; ++n) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
-    // O += P V : P from the score registers, V^T rows are the B operand
+      for (int n = 0; n < VDIM / 8; ++n) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+      // O += P V : P from the score registers, V^T rows are the B operand
 #pragma unroll
-    for (int kk = 0; kk < BN / 16; ++kk) {
-      unsigned pa[4];
-      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      for (int kk = 0; kk < HN / 16; ++kk) {
+        unsigned pa[4];
+        pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-      for (int np = 0; np < VDIM / 16; ++np) {
-        unsigned bfr[4];
-        const int row = np * 16 + (lane >> 4) * 8 + (lane & 7), chunk = kk * 2 + ((lane >> 3) & 1);
-        ldmatrix_x4(bfr, Vb + row * BN + swz<BN>(row, chunk) * 8);
-        mma_bf16(o[2 * np], pa, bfr[0], bfr[1]);
-        mma_bf16(o[2 * np + 1], pa, bfr[2], bfr[3]);
+        for (int np = 0; np < VDIM / 16; ++np) {
+          unsigned bfr[4];
+          const int row = np * 16 + (lane >> 4) * 8 + (lane & 7), chunk = (half * (HN / 16) + kk) * 2 + ((lane >> 3) & 1);
+          ldmatrix_x4(bfr, Vb + row * BN + swz<BN>(row, chunk) * 8);
+          mma_bf16(o[2 * np], pa, bfr[0], bfr[1]);
+          mma_bf16(o[2 * np + 1], pa, bfr[2], bfr[3]);
+        }
       }
     }
     __syncthreads();   // the buffer is refilled two iterations on
@@ -311,16 +314,21 @@ extern "C" int tl_sink_attn_mma(const void* q, const void* k_pages, const void* 
 // Steps of few tokens.  part: [T][nkv][splits][group][VDIM + 2] floats: output sums, then maximum (log2
 // units) and sum of the share; a share without visible keys leaves maximum -inf and sum 0.
 // ---------------------------------------------------------------------------------------------------
-#define SPLIT_MAX_GROUP 8
+#define SPLIT_MAX_GROUP 16
 
+// The 16 rows of the tensor-core tile are the query heads of one key/value head's group (rows beyond the
+// group are zero); each of the four warps takes 16 of a page's 64 keys, with its own running maximum and
+// sum, and the four are joined in shared memory at the end.
 __global__ void __launch_bounds__(THREADS)
 sink_attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                        float* __restrict__ part, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                        const int* __restrict__ seq_slot, const int* __restrict__ page_table, int table_stride, int nh,
                        int nkv, int window, int keep_first, float scale, float cap, int splits) {
-  __shared__ float qs[SPLIT_MAX_GROUP][DIM];
-  __shared__ float sc[SPLIT_MAX_GROUP][BN];
-  __shared__ float alpha_s[SPLIT_MAX_GROUP], m_s[SPLIT_MAX_GROUP], l_s[SPLIT_MAX_GROUP];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                // [2][BN][DIM]
+  bf16* Vs = Ks + 2 * BN * DIM;                                 // [2][VDIM][BN]
+  __shared__ __align__(16) bf16 Qs[16 * DIM];
+  __shared__ float wm[4][16], wl[4][16];
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
@@ -331,105 +339,147 @@ sink_attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
   const TilePages tp = tile_pages(pos, pos, window, keep_first);
   const int per = (tp.n_iter + splits - 1) / splits;
   const int i0 = sp * per, i1 = (i0 + per < tp.n_iter) ? i0 + per : tp.n_iter;
-  for (int i = tid; i < group * DIM; i += THREADS)
-    qs[i / DIM][i % DIM] = __bfloat162float(q[((size_t)t * nh + kvh * group) * DIM + i]);
-  if (tid < SPLIT_MAX_GROUP) { m_s[tid] = -INFINITY; l_s[tid] = 0.0f; }
-  __syncthreads();
-  float acc[SPLIT_MAX_GROUP];
-#pragma unroll
-  for (int g = 0; g < SPLIT_MAX_GROUP; ++g) acc[g] = 0.0f;
-  const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
-  const int sub = lane & 7, kq = lane >> 3;             // 8 lanes share a key; a warp takes 4 keys at a time
-  for (int it = i0; it < i1; ++it) {
-    const int col = tp.col(it);
-    const int page = table[col];
-    const bf16* kb = k_pages + ((size_t)page * nkv + kvh) * BN * DIM;
-    // scores of the page's 64 keys for every head of the group
-    for (int kbase = warp * 16; kbase < warp * 16 + 16; kbase += 4) {
-      const int key = kbase + kq;
-      float dot[SPLIT_MAX_GROUP];
-#pragma unroll
-      for (int g = 0; g < SPLIT_MAX_GROUP; ++g) dot[g] = 0.0f;
-      for (int c = sub; c < DIM / 8; c += 8) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(kb + (size_t)key * DIM + c * 8);
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        float kv[8];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); kv[2 * e] = f.x; kv[2 * e + 1] = f.y; }
-#pragma unroll
-        for (int g = 0; g < SPLIT_MAX_GROUP; ++g)
-          if (g < group) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) dot[g] = fmaf(qs[g][c * 8 + e], kv[e], dot[g]);
-          }
-      }
-#pragma unroll
-      for (int g = 0; g < SPLIT_MAX_GROUP; ++g)
-        if (g < group) {
-          float d = dot[g];
-          d += __shfl_xor_sync(0xffffffffu, d, 1);
-          d += __shfl_xor_sync(0xffffffffu, d, 2);
-          d += __shfl_xor_sync(0xffffffffu, d, 4);
-          if (sub == 0) {
-            const int j = col * TL_PAGE + key;
-            float v = d * scale;
-            if (cap > 0.0f) v = cap * tanhf(v * inv_cap);
-            const bool vis = j <= pos && (window <= 0 || pos - j < window || j < keep_first);
-            sc[g][key] = vis ? v * LOG2E : -INFINITY;
-          }
-        }
+  auto load_page = [&](int it, int buf) {
+    const int page = table[tp.col(it)];
+    load_tile_async<DIM, BN, THREADS>(Ks + buf * BN * DIM, k_pages + ((size_t)page * nkv + kvh) * BN * DIM, tid);
+    load_tile_async<BN, VDIM, THREADS>(Vs + buf * VDIM * BN, v_pages + ((size_t)page * nkv + kvh) * VDIM * BN, tid);
+  };
+  if (i0 < i1) load_page(i0, 0);
+  cp_async_commit();
+  {
+    constexpr int C = DIM / 8;
+    for (int i = tid; i < 16 * C; i += THREADS) {
+      const int row = i / C, chunk = i - row * C;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (row < group) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nh + kvh * group + row) * DIM + chunk * 8);
+      *reinterpret_cast<uint4*>(Qs + row * DIM + swz<DIM>(row, chunk) * 8) = v;
     }
-    __syncthreads();
-    // running maximum and sum per head; the scores become weights
-    for (int g = warp; g < group; g += THREADS / 32) {
-      const float s0 = sc[g][lane], s1 = sc[g][lane + 32];
-      const float mx = warp_max(fmaxf(s0, s1));
-      const float m_old = m_s[g];
-      const float m_new = fmaxf(m_old, mx);
-      const float base = m_new == -INFINITY ? 0.0f : m_new;
-      const float p0 = exp2f(s0 - base), p1 = exp2f(s1 - base);
-      const float sum = warp_sum(p0 + p1);
-      sc[g][lane] = p0;
-      sc[g][lane + 32] = p1;
-      if (lane == 0) {
-        const float a = m_new == -INFINITY ? 0.0f : exp2f(m_old - m_new);
-        alpha_s[g] = a;
-        l_s[g] = l_s[g] * a + sum;
-        m_s[g] = m_new;
-      }
-    }
-    __syncthreads();
-    if (tid < VDIM) {
-      const bf16* vb = v_pages + (((size_t)page * nkv + kvh) * VDIM + tid) * BN;
-#pragma unroll
-      for (int g = 0; g < SPLIT_MAX_GROUP; ++g) acc[g] *= g < group ? alpha_s[g] : 0.0f;
-#pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(vb + c * 8);
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        float vv[8];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); vv[2 * e] = f.x; vv[2 * e + 1] = f.y; }
-#pragma unroll
-        for (int g = 0; g < SPLIT_MAX_GROUP; ++g)
-          if (g < group) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[g] = fmaf(sc[g][c * 8 + e], vv[e], acc[g]);
-          }
-      }
-    }
-    __syncthreads();   // sc is rewritten by the next page
   }
-  float* dst = part + ((((size_t)t * nkv + kvh) * splits + sp) * group) * (VDIM + 2);
+  __syncthreads();
+  unsigned qf[DIM / 16][4];
 #pragma unroll
-  for (int g = 0; g < SPLIT_MAX_GROUP; ++g)
-    if (g < group) {
-      if (tid < VDIM) dst[(size_t)g * (VDIM + 2) + tid] = acc[g];
-      if (tid == 0) {
-        dst[(size_t)g * (VDIM + 2) + VDIM] = m_s[g];
-        dst[(size_t)g * (VDIM + 2) + VDIM + 1] = l_s[g];
+  for (int kk = 0; kk < DIM / 16; ++kk) {
+    const int row = lane & 15, chunk = kk * 2 + (lane >> 4);
+    ldmatrix_x4(qf[kk], Qs + row * DIM + swz<DIM>(row, chunk) * 8);
+  }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+  float o[VDIM / 8][4];
+#pragma unroll
+  for (int n = 0; n < VDIM / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+  const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
+  const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
+  for (int it = i0; it < i1; ++it) {
+    const int buf = (it - i0) & 1;
+    if (it + 1 < i1) load_page(it + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const bf16* Kb = Ks + buf * BN * DIM;
+    const bf16* Vb = Vs + buf * VDIM * BN;
+    const int key0 = tp.col(it) * TL_PAGE + warp * 16;
+    float s[2][4];
+    s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < DIM / 16; ++kk) {
+      unsigned bfr[4];
+      const int row = warp * 16 + (lane >> 4) * 8 + (lane & 7), chunk = kk * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(bfr, Kb + row * DIM + swz<DIM>(row, chunk) * 8);
+      mma_bf16(s[0], qf[kk], bfr[0], bfr[1]);
+      mma_bf16(s[1], qf[kk], bfr[2], bfr[3]);
+    }
+    float mx = -INFINITY;        // every row sees the same keys: one mask, but a maximum per row
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = key0 + n * 8 + (lane & 3) * 2 + (e & 1);
+        float v = cap > 0.0f ? cap2 * tanh_fast(s[n][e] * scale * inv_cap) : s[n][e] * scale2;
+        const bool vis = j <= pos && (window <= 0 || pos - j < window || j < keep_first);
+        v = vis ? v : -INFINITY;
+        s[n][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
       }
     }
+    (void)mx;
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    const float a0 = n0 == -INFINITY ? 0.0f : exp2f(m0 - n0), a1 = n1 == -INFINITY ? 0.0f : exp2f(m1 - n1);
+    const float b0 = n0 == -INFINITY ? 0.0f : n0, b1 = n1 == -INFINITY ? 0.0f : n1;
+    float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      s[n][0] = exp2f(s[n][0] - b0); s[n][1] = exp2f(s[n][1] - b0);
+      s[n][2] = exp2f(s[n][2] - b1); s[n][3] = exp2f(s[n][3] - b1);
+      sum0 += s[n][0] + s[n][1];
+      sum1 += s[n][2] + s[n][3];
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    l0 = l0 * a0 + sum0; l1 = l1 * a1 + sum1;
+    m0 = n0; m1 = n1;
+    unsigned pa[4];
+    pa[0] = pack_bf16(s[0][0], s[0][1]);
+    pa[1] = pack_bf16(s[0][2], s[0][3]);
+    pa[2] = pack_bf16(s[1][0], s[1][1]);
+    pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+    for (int np = 0; np < VDIM / 16; ++np) {
+      o[2 * np][0] *= a0; o[2 * np][1] *= a0; o[2 * np][2] *= a1; o[2 * np][3] *= a1;
+      o[2 * np + 1][0] *= a0; o[2 * np + 1][1] *= a0; o[2 * np + 1][2] *= a1; o[2 * np + 1][3] *= a1;
+      unsigned bfr[4];
+      const int row = np * 16 + (lane >> 4) * 8 + (lane & 7), chunk = warp * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(bfr, Vb + row * BN + swz<BN>(row, chunk) * 8);
+      mma_bf16(o[2 * np], pa, bfr[0], bfr[1]);
+      mma_bf16(o[2 * np + 1], pa, bfr[2], bfr[3]);
+    }
+    __syncthreads();   // this page's buffer is refilled two rounds on
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // join the four warps' shares of the keys: [warp][row][VDIM] sums over the page buffers
+  float* Om = reinterpret_cast<float*>(smem_raw);
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+#pragma unroll
+    for (int n = 0; n < VDIM / 8; ++n) {
+      const int c = n * 8 + (lane & 3) * 2;
+      Om[(warp * 16 + r0) * VDIM + c] = o[n][0];
+      Om[(warp * 16 + r0) * VDIM + c + 1] = o[n][1];
+      Om[(warp * 16 + r1) * VDIM + c] = o[n][2];
+      Om[(warp * 16 + r1) * VDIM + c + 1] = o[n][3];
+    }
+    if ((lane & 3) == 0) {
+      wm[warp][r0] = m0; wl[warp][r0] = l0;
+      wm[warp][r1] = m1; wl[warp][r1] = l1;
+    }
+  }
+  __syncthreads();
+  float* dst = part + ((((size_t)t * nkv + kvh) * splits + sp) * group) * (VDIM + 2);
+  for (int g = 0; g < group; ++g) {
+    const float M = fmaxf(fmaxf(wm[0][g], wm[1][g]), fmaxf(wm[2][g], wm[3][g]));
+    float f[4], l = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      f[w] = wm[w][g] == -INFINITY ? 0.0f : exp2f(wm[w][g] - M);
+      l += wl[w][g] * f[w];
+    }
+    for (int c = tid; c < VDIM; c += THREADS) {
+      float a = 0.0f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) a += Om[(w * 16 + g) * VDIM + c] * f[w];
+      dst[(size_t)g * (VDIM + 2) + c] = a;
+    }
+    if (tid == 0) {
+      dst[(size_t)g * (VDIM + 2) + VDIM] = M;
+      dst[(size_t)g * (VDIM + 2) + VDIM + 1] = l;
+    }
+  }
 }
 
 __global__ void __launch_bounds__(THREADS)
@@ -468,7 +518,15 @@ extern "C" int tl_sink_attn_split(const void* q, const void* k_pages, const void
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > SPLIT_MAX_GROUP || nh > 65535 || nkv > 65535 || splits < 1 ||
       splits > 65535 || part == nullptr)
     return TL_ERR_UNSUPPORTED;
-  const int rc = tl_launch(sink_attn_split_kernel, dim3(T, nkv, splits), dim3(THREADS), 0, stream, (const bf16*)q,
+  const size_t smem = (size_t)(2 * BN * DIM + 2 * VDIM * BN) * sizeof(bf16);
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(sink_attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return TL_ERR_UNSUPPORTED;
+    set = true;
+  }
+  const int rc = tl_launch(sink_attn_split_kernel, dim3(T, nkv, splits), dim3(THREADS), smem, stream, (const bf16*)q,
                            (const bf16*)k_pages, (const bf16*)v_pages, part, token_pos, token_seq, seq_slot,
                            page_table, table_stride, nh, nkv, window, keep_first, scale, cap, splits);
   if (rc != 0) return rc;
