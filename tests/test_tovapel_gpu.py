@@ -470,7 +470,7 @@ def test_head_norm_with_gate(dtype, H, vdim):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,H", [(1, 40), (3, 96), (4, 320), (8, 72), (2, 4100)])
+@pytest.mark.parametrize("S,H", [(1, 40), (3, 96), (4, 320), (8, 72), (2, 4100), (7, 64)])
 def test_streams_are_read_written_and_summed(dtype, S, H):
     o = _ops(dtype)
     rng = np.random.default_rng(S * H)

@@ -137,7 +137,7 @@ hc_write_kernel(float* __restrict__ xs, const float* __restrict__ M, const float
   __shared__ float m_s[HC_MAX_STREAMS * HC_MAX_STREAMS], b_s[HC_MAX_STREAMS], a_s[HC_MAX_STREAMS];
   pdl_wait();
   pdl_launch_dependents();
-  if (threadIdx.x < S * S) m_s[threadIdx.x] = M[threadIdx.x];
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) m_s[i] = M[i];
   if (threadIdx.x < S) {
     b_s[threadIdx.x] = b[threadIdx.x];
     a_s[threadIdx.x] = a2 != nullptr ? a2[threadIdx.x] : 0.0f;
