@@ -11,6 +11,11 @@
 // group of columns); a warp owns GLA_COLS columns, its lanes share the rows (row i = lane + 32 r),
 // and the tokens of a sequence are walked in order, GLA_PF at a time so that their loads and the
 // transcendental work of their decays are in flight together.
+//
+// These kernels run long, so they let the kernel after them go (programmatic dependent launch) only when
+// their main loop is done: a dependent grid that is let go at once sits on the SMs waiting, and its many
+// warps took half of the issue slots from a recurrence's few (the four kernels of a long step took 350 us
+// in sequence against 177 us each alone, and take 165 us this way).
 #include "common.cuh"
 
 #define GLA_COLS 4
@@ -42,7 +47,6 @@ __device__ __forceinline__ float gla_warp_sum4(const float (&part)[GLA_COLS], in
 __global__ void gla_decay_kernel(float* __restrict__ za, int lda, const float* __restrict__ bias, float inv_tau,
                                  int T, int hd) {
   pdl_wait();
-  pdl_launch_dependents();
   const size_t total = (size_t)T * hd;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -62,7 +66,6 @@ gla_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zk, cons
                 const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int heads, int dim,
                 int vdim) {
   pdl_wait();
-  pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = (blockIdx.z * GLA_WARPS + warp) * GLA_COLS;
@@ -130,6 +133,7 @@ gla_scan_kernel(const float* __restrict__ zq, const float* __restrict__ zk, cons
       }
     }
   }
+  pdl_launch_dependents();   // the next kernel may set up while this one writes its results
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int i = lane + 32 * r;
@@ -179,7 +183,6 @@ gla_chunk_local_kernel(const float* __restrict__ zq, const float* __restrict__ z
                        float* __restrict__ cum, float* __restrict__ o, int ldo, const int* __restrict__ seq_start,
                        int B, int heads, int dim, int vdim) {
   pdl_wait();
-  pdl_launch_dependents();
   const int h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = (blockIdx.z * GLA_WARPS + warp) * GLA_COLS;
@@ -240,6 +243,7 @@ gla_chunk_local_kernel(const float* __restrict__ zq, const float* __restrict__ z
       }
     }
   }
+  pdl_launch_dependents();   // the next kernel may set up while this one writes its results
   float* E = ends + (((size_t)blockIdx.x * heads + h) * dim) * vdim;
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -264,7 +268,6 @@ gla_chunk_local_cols_kernel(const float* __restrict__ zq, const float* __restric
   constexpr int D = 32 * R;                    // rows held (dim rounded up; the rest are zero)
   __shared__ __align__(16) float sq[GLA_SUB][D], sk[GLA_SUB][D], sa[GLA_SUB][D];
   pdl_wait();
-  pdl_launch_dependents();
   const int h = blockIdx.y, tid = threadIdx.x;
   const int c = blockIdx.z * 128 + tid;
   int b, t0, n;
@@ -317,6 +320,7 @@ gla_chunk_local_cols_kernel(const float* __restrict__ zq, const float* __restric
       if (c < vdim) o[(size_t)(t0 + tb + p) * ldo + h * vdim + c] = acc0 + acc1;
     }
   }
+  pdl_launch_dependents();   // the next kernel may set up while this one writes its results
   if (c < vdim) {
     float* E = ends + (((size_t)blockIdx.x * heads + h) * dim) * vdim + c;
 #pragma unroll
@@ -332,7 +336,6 @@ gla_chunk_carry_kernel(const float* __restrict__ ends, const float* __restrict__
                        float* __restrict__ state, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                        int heads, int dim, int vdim) {
   pdl_wait();
-  pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c0 = (blockIdx.z * GLA_WARPS + warp) * GLA_COLS;
@@ -386,6 +389,7 @@ gla_chunk_carry_kernel(const float* __restrict__ ends, const float* __restrict__
         }
     }
   }
+  pdl_launch_dependents();   // the next kernel may set up while this one writes its results
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int i = lane + 32 * r;
@@ -404,7 +408,6 @@ gla_chunk_apply_kernel(const float* __restrict__ zq, int ld, const float* __rest
   __shared__ float As[16][GLA_CHUNK + 4];
   __shared__ float Bs[16][64 + 4];
   pdl_wait();
-  pdl_launch_dependents();
   const int h = blockIdx.y, n0 = blockIdx.z * 64, tid = threadIdx.x;
   int b, t0, n;
   if (!gla_find_chunk(blockIdx.x, seq_start, B, &b, &t0, &n)) return;
@@ -437,6 +440,7 @@ gla_chunk_apply_kernel(const float* __restrict__ zq, int ld, const float* __rest
     }
     __syncthreads();
   }
+  pdl_launch_dependents();   // the next kernel may set up while this one writes its results
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int m = ty * 4 + i;

@@ -164,7 +164,6 @@ moe_gemm_kernel(const act_t* __restrict__ A, int lda, const int* __restrict__ ro
   __shared__ int src_row[GBM];
   __shared__ int tile_info[3];   // expert, first row, rows
   pdl_wait();
-  pdl_launch_dependents();
   const int tid = threadIdx.x;
   if (tid == 0) {
     int tile = blockIdx.y, e = 0, found = -1;
@@ -227,6 +226,7 @@ moe_gemm_kernel(const act_t* __restrict__ A, int lda, const int* __restrict__ ro
     }
     __syncthreads();
   }
+  pdl_launch_dependents();   // only now: a grid let go earlier would sit on the SMs and take issue slots
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int m = ty * 4 + i;
@@ -355,7 +355,6 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
   __shared__ int src_row[MBM];
   __shared__ int tile_info[3];
   pdl_wait();
-  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) {
     int tile = blockIdx.y, e = 0, found = -1;
@@ -442,6 +441,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, int lda, const int* __restrict__
       }
     }
   }
+  pdl_launch_dependents();   // only now: a grid let go earlier would sit on the SMs and take issue slots
   asm volatile("cp.async.wait_group 0;");
   const int ra = warp * 16 + (lane >> 2), rb = ra + 8;
 #pragma unroll

@@ -99,7 +99,6 @@ sink_attn_kernel(const act_t* __restrict__ q, const act_t* __restrict__ k_pages,
   __shared__ int ky[SA_THREADS];   // its place in the page
   __shared__ float scratch[33];
   pdl_wait();
-  pdl_launch_dependents();
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int kvh = h / (nh / nkv);
   const int pos = token_pos[t];
@@ -157,6 +156,7 @@ sink_attn_kernel(const act_t* __restrict__ q, const act_t* __restrict__ k_pages,
     }
     __syncthreads();  // ps, pg and ky are rewritten by the next chunk
   }
+  pdl_launch_dependents();   // only now: a grid let go earlier would sit on the SMs and take issue slots
   float gv = 1.0f;
   if (gate != nullptr) gv = 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
   const float f = gv / l_run;

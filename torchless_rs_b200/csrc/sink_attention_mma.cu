@@ -119,7 +119,6 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
   bf16* Vs = Ks + 2 * BN * DIM;                                // [2][VDIM][BN]
   __shared__ int tile_info[3];
   pdl_wait();
-  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = blockIdx.y, kvh = h / (nh / nkv);
   if (tid == 0) {
@@ -276,6 +275,7 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
     }
     __syncthreads();   // the buffer is refilled two iterations on
   }
+  pdl_launch_dependents();   // only now: a grid let go earlier would sit on the SMs and take issue slots
   cp_async_wait<0>();
   float f0 = 0.0f, f1 = 0.0f;
   if (r0 < rows) f0 = (gate != nullptr ? 1.0f / (1.0f + __expf(-gate[(size_t)(t0 + r0) * ldg + h])) : 1.0f) / l0;
@@ -330,7 +330,6 @@ sink_attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
   __shared__ __align__(16) bf16 Qs[16 * DIM];
   __shared__ float wm[4][16], wl[4][16];
   pdl_wait();
-  pdl_launch_dependents();
   const int t = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int group = nh / nkv;
@@ -440,6 +439,7 @@ sink_attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pa
     }
     __syncthreads();   // this page's buffer is refilled two rounds on
   }
+  pdl_launch_dependents();   // only now: a grid let go earlier would sit on the SMs and take issue slots
   cp_async_wait<0>();
   __syncthreads();
   // join the four warps' shares of the keys: [warp][row][VDIM] sums over the page buffers
