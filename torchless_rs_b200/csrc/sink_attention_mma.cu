@@ -122,7 +122,8 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = blockIdx.y, kvh = h / (nh / nkv);
   if (tid == 0) {
-    int tile = blockIdx.x, found = -1, b = 0;
+    // the last tiles of a sequence see the most keys: they go first, so that they do not end the kernel alone
+    int tile = (int)(gridDim.x - 1 - blockIdx.x), found = -1, b = 0;
     for (; b < n_seqs; ++b) {
       const int cnt = seq_start[b + 1] - seq_start[b];
       const int tiles = (cnt + BM - 1) / BM;
