@@ -63,8 +63,10 @@ def test_errors_name_the_key():
 def test_the_model_asks_for_the_designs_tensors(name):
     exp = expected_tensors(tl.config_from_dict(CONFIGS[name]).model_spec())
     want = tensor_shapes(CONFIGS[name], DECAY_RANKS[name])
-    got = {n: tuple(s.shape) for n, s in exp.items() if not s.optional}
+    # (optional: what a layer without feed-forward does not use, and a single stream's connections)
+    got = {n: tuple(s.shape) for n, s in exp.items() if not s.optional or n in want}
     assert sorted(got) == sorted(want)
+    assert all(s.optional == (CONFIGS[name]["streams"] == 1) for n, s in exp.items() if ".hc" in n and n in want)
     for n, shape in got.items():
         # the decay map's inner size is the stored tensors' business: the model leaves it open
         assert all(a == -1 or a == b for a, b in zip(shape, want[n])) and len(shape) == len(want[n]), n

@@ -193,6 +193,30 @@ def test_a_folder_may_hold_the_unused_tensors_of_a_layer_without_feed_forward():
     assert_close(tm.step_np(s, [toks], "all"), tm.reference(toks), "float32", "unused tensors present")
 
 
+def test_a_single_stream_may_come_without_its_connections():
+    """One stream whose folder stores no connections is the plain pre-norm block: the same logits as with
+    stored connections that are all one."""
+    cfg = CONFIGS["Q"]
+    stored = make_weights(cfg, 9, torch.float32, DECAY_RANKS["Q"])
+    ones = {k: torch.ones_like(v) for k, v in stored.items() if ".hc" in k}
+    toks = tokens_of(np.random.default_rng(0), 40, cfg["vocab"])
+    with_ones = TModel(cfg, "float32", weights={**stored, **ones})
+    s = with_ones.engine.start_sequences(1)
+    ref = with_ones.step_np(s, [toks], "all")
+    assert_close(ref, with_ones.reference(toks), "float32", "connections of ones")
+    bare = {k: v for k, v in stored.items() if ".hc" not in k}
+    import shutil
+    import torchless_rs_b200 as tl
+    d = write_folder(cfg, bare)
+    try:
+        model = tl.load(d, dtype="float32", max_tokens=256)
+    finally:
+        shutil.rmtree(d, ignore_errors=True)
+    s = model.engine.start_sequences(1)
+    got = model.engine.step(s, [toks], "all").float().cpu().numpy()
+    assert np.array_equal(got, ref)
+
+
 def test_replay_program_and_command_line(tmp_path):
     from test_trace_run_gpu import collect, run_trace
     cfg = CONFIGS["P"]

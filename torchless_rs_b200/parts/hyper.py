@@ -60,18 +60,26 @@ class HyperConnectionBlock:
         S = int(spec.params["streams"])
         names = tuple(spec.params.get("names") or ("hc1", "hc2"))[:len(cls.sublayers)]
         out = {}
+        # with one stream and no stored connections the block is the plain pre-norm block (all ones)
+        opt = S == 1
         for n in names:
-            out[f"{prefix}.{n}.in"] = TensorSpec((S,), init=(0.2, 1.0 / S))
-            out[f"{prefix}.{n}.out"] = TensorSpec((S,), init=(0.2, 1.0))
-            out[f"{prefix}.{n}.mix"] = TensorSpec((S, S), init=(0.2, 1.0 / S))
+            out[f"{prefix}.{n}.in"] = TensorSpec((S,), init=(0.2, 1.0 / S), optional=opt)
+            out[f"{prefix}.{n}.out"] = TensorSpec((S,), init=(0.2, 1.0), optional=opt)
+            out[f"{prefix}.{n}.mix"] = TensorSpec((S, S), init=(0.2, 1.0 / S), optional=opt)
         return out
 
     def load(self, weights: Dict[str, torch.Tensor]) -> None:
-        f32 = lambda t: t.to(device=self.rt.device, dtype=torch.float32).contiguous()
+        S = self.streams
+
+        def f32(name, shape):
+            t = weights.get(name)
+            if t is None:      # only a single stream may come without its connections
+                return torch.ones(shape, dtype=torch.float32, device=self.rt.device)
+            return t.to(device=self.rt.device, dtype=torch.float32).contiguous()
         for n in self.names:
-            self.read.append(f32(weights[f"{self.prefix}.{n}.in"]))
-            self.mix.append(f32(weights[f"{self.prefix}.{n}.mix"]))
-            self.write.append(f32(weights[f"{self.prefix}.{n}.out"]))
+            self.read.append(f32(f"{self.prefix}.{n}.in", (S,)))
+            self.mix.append(f32(f"{self.prefix}.{n}.mix", (S, S)))
+            self.write.append(f32(f"{self.prefix}.{n}.out", (S,)))
         self._norm_list = [self.norms[r] for r in self.norm_roles]
         for norm in self._norm_list:
             if norm.weight.dtype != torch.float32:
