@@ -2,8 +2,10 @@
 // (what it computes: sink_attention.cu), for one pair of key and value sizes per library
 // (-DSA_DIM, -DSA_VDIM, multiples of 16 up to 128).
 //
-//   sink_attn_mma_kernel     steps of many tokens: a block takes 128 consecutive tokens of one sequence
-//                            and one query head, a warp 16 of them; keys and values come page by page (64 keys) into
+//   sink_attn_mma_kernel     steps of many tokens: a block takes 64 consecutive tokens of one sequence
+//                            and one query head; a warp takes 16 of them and one half of every page's
+//                            keys (eight warps: four groups of rows times two halves, joined at the
+//                            end), so that the chain of pages a tile walks costs half as much; keys and values come page by page (64 keys) into
 //                            shared memory with cp.async, two pages in flight; Q K^T and P V on the
 //                            tensor cores (mma.sync m16n8k16, fragments by ldmatrix from swizzled
 //                            tiles: a key page is the B operand as it lies, and so is the transposed
@@ -31,7 +33,7 @@
 #endif
 
 constexpr int DIM = SA_DIM, VDIM = SA_VDIM;
-constexpr int BM = 128, BN = TL_PAGE, THREADS = 128, MMA_THREADS = 256;
+constexpr int BM = 64, BN = TL_PAGE, THREADS = 128, MMA_THREADS = 256;
 static_assert(TL_PAGE == 64, "a page is one key tile of 64");
 static_assert(DIM % 16 == 0 && VDIM % 16 == 0 && DIM >= 16 && VDIM >= 16 && DIM <= 128 && VDIM <= 128, "sizes");
 #define LOG2E 1.4426950408889634f
@@ -163,19 +165,21 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
   load_page(0, 0);
   cp_async_commit();
 
-  const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;          // the two rows this thread holds
+  const int rg = warp & 3, kh = warp >> 2;                      // group of 16 rows, half of a page's keys
+  const int r0 = rg * 16 + (lane >> 2), r1 = r0 + 8;            // the two rows this thread holds
   const int pos0 = r0 < rows ? p_first + r0 : -1, pos1 = r1 < rows ? p_first + r1 : -1;
-  const float sk = sink != nullptr ? sink[h] * LOG2E : -INFINITY;
+  // the sink is counted once: it opens the first halves' maximum and sum
+  const float sk = (sink != nullptr && kh == 0) ? sink[h] * LOG2E : -INFINITY;
   float m0 = sk, m1 = sk;
-  float l0 = sink != nullptr ? 1.0f : 0.0f, l1 = l0;
+  float l0 = (sink != nullptr && kh == 0) ? 1.0f : 0.0f, l1 = l0;
   float o[VDIM / 8][4];
 #pragma unroll
   for (int n = 0; n < VDIM / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
   const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
   const float cap2 = cap * LOG2E, scale2 = scale * LOG2E;
   // what this warp's 16 rows span; a warp without rows only helps to load
-  const int wrows = rows - warp * 16;
-  const int wp_first = p_first + warp * 16, wp_last = wp_first + (wrows < 16 ? wrows : 16) - 1;
+  const int wrows = rows - rg * 16;
+  const int wp_first = p_first + rg * 16, wp_last = wp_first + (wrows < 16 ? wrows : 16) - 1;
 
   for (int it = 0; it < tp.n_iter; ++it) {
     const int buf = it & 1;
@@ -186,18 +190,17 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
     const bf16* Kb = Ks + buf * BN * DIM;
     const bf16* Vb = Vs + buf * VDIM * BN;
     const int key0 = tp.col(it) * TL_PAGE;
-    // a page that none of the warp's rows sees (keys after its last row, or before its first row's window
-    // and not kept) is passed over; a page that all of them see whole needs no mask
-    const bool none = wrows <= 0 || key0 > wp_last ||
-                      (window > 0 && wp_first - (key0 + BN - 1) >= window && key0 >= keep_first);
+    constexpr int HN = BN / 2;                   // keys per half
+    const int half = kh;
+    const int kbeg = key0 + half * HN, kend = kbeg + HN - 1;     // this warp's keys of the page
+    // keys that none of the warp's rows sees (after its last row, or before its first row's window and
+    // not kept) are passed over; keys that all of them see need no mask
+    const bool none = wrows <= 0 || kbeg > wp_last ||
+                      (window > 0 && wp_first - kend >= window && kbeg >= keep_first);
     if (none) { __syncthreads(); continue; }
-    const bool whole = wrows >= 16 && key0 + BN - 1 <= wp_first &&
-                       (window <= 0 || wp_last - key0 < window || key0 + BN - 1 < keep_first);
-    // the page in two halves of 32 keys, each with its own step of the running maximum and sum: half as
-    // many score registers, so that two blocks fit an SM
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      constexpr int HN = BN / 2;                 // keys per half
+    const bool whole = wrows >= 16 && kend <= wp_first &&
+                       (window <= 0 || wp_last - kbeg < window || kend < keep_first);
+    {
       // S = Q K^T : 16 rows x 32 keys per warp
       float s[HN / 8][4];
 #pragma unroll
@@ -206,7 +209,7 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
       for (int kk = 0; kk < DIM / 16; ++kk) {
         unsigned qa[4];
         {
-          const int row = warp * 16 + (lane & 15), chunk = kk * 2 + (lane >> 4);
+          const int row = rg * 16 + (lane & 15), chunk = kk * 2 + (lane >> 4);
           ldmatrix_x4(qa, Qs + row * DIM + swz<DIM>(row, chunk) * 8);
         }
 #pragma unroll
@@ -278,6 +281,38 @@ sink_attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_page
   }
   pdl_launch_dependents();   // only now: a grid let go earlier would sit on the SMs and take issue slots
   cp_async_wait<0>();
+  __syncthreads();
+  // the second halves hand their sums to the first through the page buffers: [BM][VDIM] floats
+  float* Om = reinterpret_cast<float*>(smem_raw);
+  __shared__ float pm[BM], pl[BM];
+  if (kh == 1) {
+    const int a = rg * 16 + (lane >> 2), b2 = a + 8;
+#pragma unroll
+    for (int n = 0; n < VDIM / 8; ++n) {
+      const int c = n * 8 + (lane & 3) * 2;
+      Om[a * VDIM + c] = o[n][0]; Om[a * VDIM + c + 1] = o[n][1];
+      Om[b2 * VDIM + c] = o[n][2]; Om[b2 * VDIM + c + 1] = o[n][3];
+    }
+    if ((lane & 3) == 0) { pm[a] = m0; pl[a] = l0; pm[b2] = m1; pl[b2] = l1; }
+  }
+  __syncthreads();
+  if (kh == 1) return;
+  {
+    const float ma = pm[r0], mb = pm[r1];
+    const float M0 = fmaxf(m0, ma), M1 = fmaxf(m1, mb);
+    const float fa0 = m0 == -INFINITY ? 0.0f : exp2f(m0 - M0), fb0 = ma == -INFINITY ? 0.0f : exp2f(ma - M0);
+    const float fa1 = m1 == -INFINITY ? 0.0f : exp2f(m1 - M1), fb1 = mb == -INFINITY ? 0.0f : exp2f(mb - M1);
+    l0 = l0 * fa0 + pl[r0] * fb0;
+    l1 = l1 * fa1 + pl[r1] * fb1;
+#pragma unroll
+    for (int n = 0; n < VDIM / 8; ++n) {
+      const int c = n * 8 + (lane & 3) * 2;
+      o[n][0] = o[n][0] * fa0 + Om[r0 * VDIM + c] * fb0;
+      o[n][1] = o[n][1] * fa0 + Om[r0 * VDIM + c + 1] * fb0;
+      o[n][2] = o[n][2] * fa1 + Om[r1 * VDIM + c] * fb1;
+      o[n][3] = o[n][3] * fa1 + Om[r1 * VDIM + c + 1] * fb1;
+    }
+  }
   float f0 = 0.0f, f1 = 0.0f;
   if (r0 < rows) f0 = (gate != nullptr ? 1.0f / (1.0f + __expf(-gate[(size_t)(t0 + r0) * ldg + h])) : 1.0f) / l0;
   if (r1 < rows) f1 = (gate != nullptr ? 1.0f / (1.0f + __expf(-gate[(size_t)(t0 + r1) * ldg + h])) : 1.0f) / l1;
